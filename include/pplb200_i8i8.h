@@ -1,0 +1,176 @@
+/*
+ * C ABI of the B200 (sm_100a) W8A8 "i8i8" linear path.
+ *
+ * Every entry point is stream-ordered and asynchronous, allocates nothing, and
+ * returns a ppl.common RetCode value (0 success, 2 unsupported, 4 invalid value,
+ * 10 device runtime error).  All pointers are device pointers unless a comment
+ * says otherwise; the caller owns every buffer, stream and communicator.
+ * Matrix layouts use the reference's matrix_layout_t numbering
+ * (include/ppl/kernel/llm/cuda/common/matrix_layout.h:25-31).
+ *
+ * The C++ operator API of the reference (namespace ppl::kernel::llm::cuda) is
+ * provided on top of this ABI as header-inline forwards under
+ * include/ppl/kernel/llm/cuda/, so no C++ ABI crosses the shared library.
+ */
+#ifndef PPLB200_I8I8_H
+#define PPLB200_I8I8_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef struct CUstream_st* pplb200_stream_t; /* == cudaStream_t */
+
+/* epilogue modes of pplb200_i8i8_gemm */
+enum {
+    PPLB200_EPI_RAW_I32 = 0,          /* out = int32 accumulators [M, N]                                  */
+    PPLB200_EPI_DEQUANT_F16 = 1,      /* out = fp16 (acc * scale_N * down_N * scale_M * down_M) + bias   */
+    PPLB200_EPI_DEQUANT_F16_REQUANT_I8 = 2 /* as 1, plus out_q/out_q_scale = per-token quantize(out)    */
+};
+
+/* Library / build identification: "pplb200 i8i8 <version> sm_100a". */
+const char* pplb200_version(void);
+
+/* Last error text recorded by a failing call on the calling thread ("" if none). */
+const char* pplb200_last_error(void);
+
+/*
+ * Per-token dynamic symmetric quantizer, fp16 -> int8.
+ * Replaces ppl::kernel::llm::cuda::pmx::i8i8::minmax_quantize_fp16
+ *   (include/ppl/kernel/llm/cuda/pmx/i8i8/quantize.h:32-41; src/.../pmx/i8i8/quantize.cu:27-124).
+ * in fp16 [batch, quant_dim] row-major; q int8 [batch, quant_dim] in `to_layout`
+ * (ROW_MAJOR, COL32 or COL32_2R_4R4); scale fp16 [batch] = scale * up_scale.
+ * Requires quant_dim % 16 == 0 and 16-byte aligned in/q.
+ */
+int32_t pplb200_i8i8_minmax_quantize_fp16(pplb200_stream_t stream, const void* in, int64_t batch, int64_t quant_dim,
+                                          float up_scale, int32_t to_layout, void* q, void* scale);
+
+/*
+ * int32 -> fp16 dequantize with row scale x column scale and optional fp16 bias.
+ * Replaces ppl::kernel::llm::cuda::pmx::i8i8::minmax_dequantize_fp16
+ *   (include/.../pmx/i8i8/quantize.h:43-55; src/.../pmx/i8i8/quantize.cu:126-234).
+ * acc int32 [batch, quant_dim] in `from_layout` (any of the five layouts); out fp16 row-major.
+ * Requires quant_dim % 4 == 0 (RC_INVALID_VALUE otherwise, as the reference).
+ */
+int32_t pplb200_i8i8_minmax_dequantize_fp16(pplb200_stream_t stream, const void* acc, const void* optional_bias,
+                                            const void* scale_per_batch, const void* scale_per_channel,
+                                            int64_t batch, int64_t quant_dim, float down_scale_batch,
+                                            float down_scale_channel, int32_t from_layout, void* out);
+
+/*
+ * Scratch bytes pplb200_i8i8_gemm needs for (M, N, K, mode).  0 means `ws` may be NULL.
+ */
+int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode);
+
+/*
+ * C[M,N] = A[M,K] (int8, row-major, lda) x B[N,K]^T (int8, row-major, ldb) on tcgen05 tensor
+ * cores with int32 TMEM accumulators, plus the fused epilogue selected by `epilogue_mode`.
+ * Replaces ppl::kernel::llm::cuda::cublas::gemm_i8i8i32
+ *   (include/.../cublas/gemm.h:56-79; src/.../cublas/gemm.cu:171-363) and, for modes 1/2, the
+ *   minmax_dequantize_fp16 launch that follows it in the linear ops
+ *   (src/.../pmx/i8i8/column_parallel_linear.cu:136-157).
+ * Requires K % 16 == 0, lda % 16 == 0, ldb % 16 == 0, N % 8 == 0, 16-byte aligned A, B, out.
+ * out: int32 [M, ldc] (mode 0) or fp16 [M, ldc] (modes 1, 2).
+ * Mode 2 also writes out_q int8 [M, N] and out_q_scale fp16 [M] = scale * requant_up_scale, where
+ * (out_q, scale) = per-token quantize of the fp16 `out` rows; it needs `ws` of
+ * pplb200_i8i8_gemm_workspace_bytes() bytes (contents need not be initialised).
+ */
+int32_t pplb200_i8i8_gemm(pplb200_stream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb,
+                          int64_t M, int64_t N, int64_t K, int32_t epilogue_mode,
+                          const void* scale_M, const void* scale_N, const void* optional_bias,
+                          float down_scale_M, float down_scale_N, float requant_up_scale,
+                          void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q, void* out_q_scale);
+
+/*
+ * Scratch bytes pplb200_i8i8_linear_fp16 needs (quantized activations, row scales, GEMM scratch).
+ */
+int64_t pplb200_i8i8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode);
+
+/*
+ * Whole single-device path: y = dequant( quantize(x) x W^T ) (+ bias) [-> re-quantize].
+ * x fp16 [M,K]; W int8 [N,K] row-major; scale_N fp16 [N] (up-scaled by 1/down_scale_N); bias fp16 [N] or NULL.
+ * Equivalent to minmax_quantize_fp16 followed by column_parallel_linear(gather_output = true, size 1)
+ *   (src/.../pmx/i8i8/quantize.cu:82; src/.../pmx/i8i8/column_parallel_linear.cu:29-182).
+ * epilogue_mode is PPLB200_EPI_DEQUANT_F16 or PPLB200_EPI_DEQUANT_F16_REQUANT_I8.
+ */
+int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const void* W, const void* scale_N,
+                                 const void* optional_bias, int64_t M, int64_t N, int64_t K,
+                                 float up_scale, float down_scale_M, float down_scale_N,
+                                 int32_t epilogue_mode, float requant_up_scale,
+                                 void* ws, int64_t ws_bytes, void* y, void* y_q, void* y_q_scale);
+
+/*
+ * Tensor-parallel linears.  `nccl_comm` is an ncclComm_t (may be NULL when size == 1).
+ *
+ * Column parallel: replaces ppl::kernel::llm::cuda::pmx::i8i8::column_parallel_linear
+ *   (include/.../pmx/i8i8/column_parallel_linear.h:33-58; src/.../pmx/i8i8/column_parallel_linear.cu:29-182).
+ * input int8 [M,K]; weight int8 [N/size, K]; scale_N / bias are the rank's slices.
+ * gather_output == 0: `output` receives RAW int32 [M, N/size] (no dequant), as the reference.
+ * gather_output != 0: fp16; size == 1 -> output [M,N]; size > 1 -> all-gather into gather_buffer
+ *   [size, M, N/size] then transpose to output [M, N].  quant_buffer is unused (the int32
+ *   accumulators never leave the chip) but accepted.
+ */
+int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream, const void* input, int64_t M,
+                                            const void* weight, const void* optional_bias,
+                                            const void* scale_M, const void* scale_N,
+                                            float down_scale_M, float down_scale_N,
+                                            int64_t in_features, int64_t out_features, int32_t weight_layout,
+                                            int32_t rank, int32_t size, void* nccl_comm,
+                                            int32_t gather_output, void* gather_buffer, void* quant_buffer,
+                                            void* ws, int64_t ws_bytes, void* output);
+
+/*
+ * Row parallel: replaces ppl::kernel::llm::cuda::pmx::i8i8::row_parallel_linear
+ *   (include/.../pmx/i8i8/row_parallel_linear.h:33-58; src/.../pmx/i8i8/row_parallel_linear.cu:28-162).
+ * input int8 [M, K/size]; weight int8 [N, K/size]; quant_buffer int32 [M, N] (required when size > 1).
+ * reduce_mode 0 (exact, default): int32 partial accumulators are summed across ranks BEFORE the
+ *   dequant epilogue, so the result is bit-identical to the unsharded linear; every rank passes
+ *   the full-row scale_M and the same bias.
+ * reduce_mode 1 (reference order): dequantize each partial to fp16, bias on rank 0 only, then fp16
+ *   all-reduce (src/.../pmx/i8i8/row_parallel_linear.cu:84,131-158).
+ */
+int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream, const void* input, int64_t M,
+                                         const void* weight, const void* optional_bias,
+                                         const void* scale_M, const void* scale_N,
+                                         float down_scale_M, float down_scale_N,
+                                         int64_t in_features, int64_t out_features, int32_t weight_layout,
+                                         int32_t rank, int32_t size, void* nccl_comm,
+                                         int32_t input_is_parallel, int32_t reduce_mode, void* quant_buffer,
+                                         void* ws, int64_t ws_bytes, void* output);
+
+/*
+ * NCCL plumbing for callers that do not already own a communicator (tests, bench).
+ * unique id: 128 bytes, host memory.  Not part of the reference surface (ppl.nn.llm creates
+ * its communicators itself and hands them over in ppl::common::NcclParam).
+ */
+int32_t pplb200_nccl_get_unique_id(void* id128_host);
+int32_t pplb200_nccl_comm_init(const void* id128_host, int32_t rank, int32_t size, void** comm_out);
+int32_t pplb200_nccl_comm_destroy(void* comm);
+
+/*
+ * Device-side health word of the GEMM kernel: every bounded wait in the kernel that gives
+ * up records a code here instead of hanging.  Returns 0 if no kernel launched on the current
+ * device has timed out since the last call with reset != 0.  Synchronises the device.
+ */
+int32_t pplb200_i8i8_gemm_status(int32_t reset);
+
+/*
+ * Host-only helper: element offset of (row, col) in a [rows, cols] matrix stored in `layout`
+ * (the index maps of include/ppl/kernel/llm/cuda/common/matrix_layout.h:34-142); -1 for an
+ * unknown layout.
+ */
+int64_t pplb200_layout_offset(int32_t layout, int64_t rows, int64_t cols, int64_t row, int64_t col);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,180 @@
+// extern "C" surface of the library (declared in include/pplb200_i8i8.h): argument checks,
+// workspace carving and the launch sequences of the single-device path.
+#include "common.cuh"
+#include "../../include/pplb200_i8i8.h"
+
+#include <stdarg.h>
+#include <string.h>
+
+namespace pplb200 {
+
+namespace {
+thread_local char g_err[512] = "";
+}
+
+int32_t fail(int32_t rc, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    fprintf(stderr, "[pplb200][ERROR] %s\n", g_err);
+    return rc;
+}
+void clear_error() { g_err[0] = '\0'; }
+
+int32_t check_launch(const char* what) {
+    const cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "%s launch failed: %s", what, cudaGetErrorString(e));
+    return RC_SUCCESS;
+}
+
+namespace {
+
+constexpr int64_t WS_ALIGN = 256;
+
+int64_t gemm_ws_bytes(int64_t M, int32_t mode) {
+    return mode == EPI_DEQUANT_F16_REQUANT_I8 ? round_up(M * 4, WS_ALIGN) : 0;
+}
+
+int32_t check_gemm_args(const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N, int64_t K,
+                        int32_t mode, const void* scale_M, const void* scale_N, const void* bias, void* out,
+                        int64_t ldc, void* out_q, void* out_q_scale) {
+    if (M < 0 || N < 0 || K <= 0) return fail(RC_INVALID_VALUE, "bad GEMM extents M=%lld N=%lld K=%lld", (long long)M, (long long)N, (long long)K);
+    if (mode < EPI_RAW_I32 || mode > EPI_DEQUANT_F16_REQUANT_I8) return fail(RC_UNSUPPORTED, "unknown epilogue mode %d", mode);
+    if (M == 0 || N == 0) return RC_SUCCESS;
+    if (!A || !B || !out) return fail(RC_INVALID_VALUE, "null A/B/out");
+    if (K % 16 || lda % 16 || ldb % 16) return fail(RC_INVALID_VALUE, "K, lda, ldb must be multiples of 16 (K=%lld lda=%lld ldb=%lld)", (long long)K, (long long)lda, (long long)ldb);
+    if (lda < K || ldb < K || ldc < N) return fail(RC_INVALID_VALUE, "leading dimension smaller than the row length");
+    if (N % 8) return fail(RC_INVALID_VALUE, "N must be a multiple of 8, got %lld", (long long)N);
+    if (!aligned16(A) || !aligned16(B) || !aligned16(out)) return fail(RC_INVALID_VALUE, "A, B and out must be 16-byte aligned");
+    const int64_t out_elem = mode == EPI_RAW_I32 ? 4 : 2;
+    if ((ldc * out_elem) % 16) return fail(RC_INVALID_VALUE, "ldc must keep rows 16-byte aligned");
+    if (mode != EPI_RAW_I32) {
+        if (!scale_M || !scale_N) return fail(RC_INVALID_VALUE, "dequant epilogue needs scale_M and scale_N");
+        if (!aligned16(scale_N) || (bias && !aligned16(bias))) return fail(RC_INVALID_VALUE, "scale_N / bias must be 16-byte aligned");
+    }
+    if (mode == EPI_DEQUANT_F16_REQUANT_I8) {
+        if (!out_q || !out_q_scale) return fail(RC_INVALID_VALUE, "re-quantize epilogue needs out_q and out_q_scale");
+        if (N % 16 || ldc != N || !aligned16(out_q)) return fail(RC_INVALID_VALUE, "re-quantize epilogue needs N %% 16 == 0, ldc == N, aligned out_q");
+    }
+    return RC_SUCCESS;
+}
+
+} // namespace
+
+int32_t gemm_entry(cudaStream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N,
+                   int64_t K, int32_t mode, const void* scale_M, const void* scale_N, const void* bias, float down_M,
+                   float down_N, float requant_up, void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q,
+                   void* out_q_scale) {
+    int32_t rc = check_gemm_args(A, lda, B, ldb, M, N, K, mode, scale_M, scale_N, bias, out, ldc, out_q, out_q_scale);
+    if (rc != RC_SUCCESS || M == 0 || N == 0) return rc;
+    GemmArgs g;
+    g.A = (const int8_t*)A; g.lda = lda; g.B = (const int8_t*)B; g.ldb = ldb;
+    g.M = M; g.N = N; g.K = K; g.mode = mode;
+    g.scale_m = (const half*)scale_M; g.scale_n = (const half*)scale_N; g.bias = (const half*)bias;
+    g.down_m = down_M; g.down_n = down_N;
+    g.out = out; g.ldc = ldc;
+    g.row_absmax_bits = nullptr;
+    if (mode == EPI_DEQUANT_F16_REQUANT_I8) {
+        const int64_t need = gemm_ws_bytes(M, mode);
+        if (!ws || ws_bytes < need) return fail(RC_INVALID_VALUE, "workspace too small: %lld < %lld", (long long)ws_bytes, (long long)need);
+        g.row_absmax_bits = (uint32_t*)ws;
+        if (cudaMemsetAsync(ws, 0, (size_t)M * 4, stream) != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
+    }
+    rc = launch_gemm(stream, g);
+    if (rc != RC_SUCCESS) return rc;
+    if (mode == EPI_DEQUANT_F16_REQUANT_I8)
+        rc = launch_quantize(stream, (const half*)out, M, N, requant_up, LAYOUT_ROW_MAJOR, (int8_t*)out_q,
+                             (half*)out_q_scale, g.row_absmax_bits);
+    return rc;
+}
+
+} // namespace pplb200
+
+using namespace pplb200;
+
+extern "C" {
+
+const char* pplb200_version(void) { return "pplb200 i8i8 0.1 sm_100a"; }
+const char* pplb200_last_error(void) { return g_err; }
+
+int32_t pplb200_i8i8_minmax_quantize_fp16(pplb200_stream_t stream, const void* in, int64_t batch, int64_t quant_dim,
+                                          float up_scale, int32_t to_layout, void* q, void* scale) {
+    if (to_layout != LAYOUT_ROW_MAJOR && to_layout != LAYOUT_COL32 && to_layout != LAYOUT_COL32_2R_4R4)
+        return fail(RC_UNSUPPORTED, "unsupported matrix layout: %d", to_layout);
+    if (batch < 0 || quant_dim < 0) return fail(RC_INVALID_VALUE, "negative extent");
+    if (batch == 0 || quant_dim == 0) return RC_SUCCESS;
+    if (quant_dim % 16) return fail(RC_INVALID_VALUE, "quant_dim must be a multiple of 16, got %lld", (long long)quant_dim);
+    if (to_layout != LAYOUT_ROW_MAJOR && quant_dim % 32) return fail(RC_INVALID_VALUE, "COL32 layouts need quant_dim %% 32 == 0");
+    if (to_layout == LAYOUT_COL32_2R_4R4 && batch % 32) return fail(RC_INVALID_VALUE, "COL32_2R_4R4 needs batch %% 32 == 0");
+    if (!in || !q || !scale) return fail(RC_INVALID_VALUE, "null pointer");
+    if (!aligned16(in) || !aligned16(q)) return fail(RC_INVALID_VALUE, "in and q must be 16-byte aligned");
+    if (batch > 0x7fffffffLL) return fail(RC_UNSUPPORTED, "batch beyond 2^31 - 1");
+    return launch_quantize((cudaStream_t)stream, (const half*)in, batch, quant_dim, up_scale, to_layout, (int8_t*)q,
+                           (half*)scale, nullptr);
+}
+
+int32_t pplb200_i8i8_minmax_dequantize_fp16(pplb200_stream_t stream, const void* acc, const void* optional_bias,
+                                            const void* scale_per_batch, const void* scale_per_channel,
+                                            int64_t batch, int64_t quant_dim, float down_scale_batch,
+                                            float down_scale_channel, int32_t from_layout, void* out) {
+    if (quant_dim % 4 != 0) return fail(RC_INVALID_VALUE, "channel must be aligned with 4, but channel = %lld", (long long)quant_dim);
+    if (from_layout < LAYOUT_ROW_MAJOR || from_layout > LAYOUT_COL4_4R2_8C) return fail(RC_UNSUPPORTED, "unsupported matrix layout: %d", from_layout);
+    if (batch < 0 || quant_dim < 0) return fail(RC_INVALID_VALUE, "negative extent");
+    if (batch == 0 || quant_dim == 0) return RC_SUCCESS;
+    if (!acc || !scale_per_batch || !scale_per_channel || !out) return fail(RC_INVALID_VALUE, "null pointer");
+    return launch_dequantize((cudaStream_t)stream, (const int32_t*)acc, (const half*)optional_bias,
+                             (const half*)scale_per_batch, (const half*)scale_per_channel, batch, quant_dim,
+                             down_scale_batch, down_scale_channel, from_layout, (half*)out);
+}
+
+int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode) {
+    (void)N; (void)K;
+    return gemm_ws_bytes(M, epilogue_mode);
+}
+
+int32_t pplb200_i8i8_gemm(pplb200_stream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb,
+                          int64_t M, int64_t N, int64_t K, int32_t epilogue_mode,
+                          const void* scale_M, const void* scale_N, const void* optional_bias,
+                          float down_scale_M, float down_scale_N, float requant_up_scale,
+                          void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q, void* out_q_scale) {
+    return gemm_entry((cudaStream_t)stream, A, lda, B, ldb, M, N, K, epilogue_mode, scale_M, scale_N, optional_bias,
+                      down_scale_M, down_scale_N, requant_up_scale, ws, ws_bytes, out, ldc, out_q, out_q_scale);
+}
+
+int64_t pplb200_i8i8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode) {
+    (void)N;
+    return round_up(M * K, WS_ALIGN) + round_up(M * 2, WS_ALIGN) + gemm_ws_bytes(M, epilogue_mode);
+}
+
+int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const void* W, const void* scale_N,
+                                 const void* optional_bias, int64_t M, int64_t N, int64_t K,
+                                 float up_scale, float down_scale_M, float down_scale_N,
+                                 int32_t epilogue_mode, float requant_up_scale,
+                                 void* ws, int64_t ws_bytes, void* y, void* y_q, void* y_q_scale) {
+    if (epilogue_mode != EPI_DEQUANT_F16 && epilogue_mode != EPI_DEQUANT_F16_REQUANT_I8)
+        return fail(RC_UNSUPPORTED, "linear_fp16 epilogue must be DEQUANT_F16 or DEQUANT_F16_REQUANT_I8");
+    if (M < 0 || N < 0 || K <= 0) return fail(RC_INVALID_VALUE, "bad extents");
+    if (M == 0 || N == 0) return RC_SUCCESS;
+    const int64_t need = pplb200_i8i8_linear_workspace_bytes(M, N, K, epilogue_mode);
+    if (!ws || ws_bytes < need) return fail(RC_INVALID_VALUE, "workspace too small: %lld < %lld", (long long)ws_bytes, (long long)need);
+    if ((reinterpret_cast<uintptr_t>(ws) & (WS_ALIGN - 1)) != 0) return fail(RC_INVALID_VALUE, "workspace must be 256-byte aligned");
+    char* base = (char*)ws;
+    void* xq = base;
+    void* sm = base + round_up(M * K, WS_ALIGN);
+    void* gws = base + round_up(M * K, WS_ALIGN) + round_up(M * 2, WS_ALIGN);
+    int32_t rc = pplb200_i8i8_minmax_quantize_fp16(stream, x, M, K, up_scale, LAYOUT_ROW_MAJOR, xq, sm);
+    if (rc != RC_SUCCESS) return rc;
+    return gemm_entry((cudaStream_t)stream, xq, K, W, K, M, N, K, epilogue_mode, sm, scale_N, optional_bias, down_scale_M,
+                      down_scale_N, requant_up_scale, gws, gemm_ws_bytes(M, epilogue_mode), y, N, y_q, y_q_scale);
+}
+
+int32_t pplb200_i8i8_gemm_status(int32_t reset) { return gemm_status(reset); }
+
+// Host helper for tests: the library's (row, col) -> offset map for a layout.
+int64_t pplb200_layout_offset(int32_t layout, int64_t rows, int64_t cols, int64_t row, int64_t col) {
+    if (layout < LAYOUT_ROW_MAJOR || layout > LAYOUT_COL4_4R2_8C) return -1;
+    return layout_offset(layout, rows, cols, row, col);
+}
+
+}

@@ -1,0 +1,90 @@
+// Shared declarations of the sm_100a i8i8 linear library: return codes, error
+// recording, small device helpers.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace pplb200 {
+
+// Numeric values of ppl::common::RetCode that this path returns.
+enum : int32_t {
+    RC_SUCCESS = 0,
+    RC_UNSUPPORTED = 2,
+    RC_INVALID_VALUE = 4,
+    RC_DEVICE_RUNTIME_ERROR = 10,
+};
+
+// matrix_layout_t numbering of the reference (common/matrix_layout.h:25-31).
+enum : int32_t {
+    LAYOUT_ROW_MAJOR = 0,
+    LAYOUT_COL_MAJOR = 1,
+    LAYOUT_COL32 = 2,
+    LAYOUT_COL32_2R_4R4 = 3,
+    LAYOUT_COL4_4R2_8C = 4,
+};
+
+enum : int32_t {
+    EPI_RAW_I32 = 0,
+    EPI_DEQUANT_F16 = 1,
+    EPI_DEQUANT_F16_REQUANT_I8 = 2,
+};
+
+// Records a message retrievable through pplb200_last_error() and returns `rc`.
+int32_t fail(int32_t rc, const char* fmt, ...);
+void clear_error();
+
+// Checks the launch status of the kernel just enqueued.
+int32_t check_launch(const char* what);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// (row, col) -> element offset in each of the reference's five layouts.
+__host__ __device__ inline int64_t layout_offset(int32_t layout, int64_t rows, int64_t cols, int64_t r, int64_t c) {
+    (void)cols;
+    switch (layout) {
+    case LAYOUT_ROW_MAJOR: return r * cols + c;
+    case LAYOUT_COL_MAJOR: return c * rows + r;
+    case LAYOUT_COL32: return ((c >> 5) * rows + r) * 32 + (c & 31);
+    case LAYOUT_COL32_2R_4R4: {
+        const int64_t rt = r & 31;
+        const int64_t slot = ((((rt & 7) >> 1) << 2) + (rt >> 3)) * 2 + (rt & 1); // 32-row interleave
+        return (c >> 5) * rows * 32 + (r >> 5) * 1024 + slot * 32 + (c & 31);
+    }
+    default: { // LAYOUT_COL4_4R2_8C
+        const int64_t cc = c & 31;
+        const int64_t line = (r & ~int64_t(7)) + ((r & 1) << 2) + (cc >> 3);
+        const int64_t quad = ((cc & 4) ? 4 : 0) + ((r & 7) >> 1);
+        return (c >> 5) * rows * 32 + line * 32 + quad * 4 + (cc & 3);
+    }
+    }
+}
+
+// ---- kernels / launchers implemented across the translation units ----
+
+int32_t launch_quantize(cudaStream_t stream, const half* in, int64_t batch, int64_t dim, float up_scale,
+                        int32_t layout, int8_t* q, half* scale, const uint32_t* given_absmax_bits);
+
+int32_t launch_dequantize(cudaStream_t stream, const int32_t* acc, const half* bias, const half* scale_m,
+                          const half* scale_n, int64_t batch, int64_t dim, float down_m, float down_n,
+                          int32_t layout, half* out);
+
+int32_t launch_transpose01_f16(cudaStream_t stream, const half* in, int64_t d0, int64_t d1, int64_t d2, half* out);
+
+struct GemmArgs {
+    const int8_t* A; int64_t lda;
+    const int8_t* B; int64_t ldb;
+    int64_t M, N, K;
+    int32_t mode;
+    const half* scale_m; const half* scale_n; const half* bias;
+    float down_m, down_n;
+    void* out; int64_t ldc;
+    uint32_t* row_absmax_bits; // mode 2: per-row max |y| as float bits, zeroed by the launcher
+};
+int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);
+int32_t gemm_status(int32_t reset);
+
+} // namespace pplb200

@@ -1,0 +1,361 @@
+// int8 x int8 -> int32 GEMM with fused dequant epilogue on the 5th-generation tensor cores
+// (tcgen05.mma kind::i8, accumulators in TMEM, operands fed by TMA into 128B-swizzled shared
+// memory).  Replaces the reference's cuBLASLt call (src/ppl/kernel/llm/cuda/cublas/gemm.cu:171-363)
+// and the dequantize launch that follows it (src/ppl/kernel/llm/cuda/pmx/i8i8/quantize.cu:126-169).
+//
+// C[M,N] = A[M,K] * B[N,K]^T, both operands K-major (row-major [rows, K]), exactly the
+// transa = false / transb = true convention of the reference's linear ops.
+//
+// Kernel shape: persistent, one CTA per SM, 6 warps:
+//   warp 0      TMA producer     (one elected lane)
+//   warp 1      MMA issuer       (one elected lane); also owns TMEM alloc / dealloc
+//   warps 2..5  epilogue         (tcgen05.ld -> scale -> fp16 -> global), one TMEM lane quarter each
+// Shared-memory ring of STAGES x {A tile 128 x 128 B, B tile BN x 128 B}; two TMEM accumulator
+// buffers of BN columns each so the epilogue of tile i overlaps the main loop of tile i + 1.
+// No TMA multicast is used anywhere.
+#include "common.cuh"
+#include "ptx.cuh"
+
+#include <mutex>
+
+namespace pplb200 {
+
+namespace {
+
+constexpr int BM = 128;       // tile rows (TMEM lanes)
+constexpr int BK = 128;       // bytes (= int8 elements) of K per stage: one 128-byte swizzle row
+constexpr int UMMA_K = 32;    // K per tcgen05.mma kind::i8
+constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARP0 = 2;
+
+// status bits recorded when a bounded wait gives up
+constexpr unsigned ST_PRODUCER_TIMEOUT = 1u, ST_MMA_FULL_TIMEOUT = 2u, ST_MMA_ACC_TIMEOUT = 4u, ST_EPI_TIMEOUT = 8u;
+
+__device__ unsigned int g_gemm_status = 0;
+
+struct KernelParams {
+    int32_t M, N;
+    int32_t num_m_tiles, num_n_tiles, num_k_blocks;
+    int32_t mode;
+    void* out; int64_t ldc;
+    const half* scale_m; const half* scale_n; const half* bias;
+    float down_m, down_n;
+    uint32_t* row_absmax_bits;
+    unsigned int* status;
+};
+
+template <int BN> struct Cfg {
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int B_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128) ? 6 : 8;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
+    static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
+    // More than half of the SM's shared memory: at most one CTA per SM, so two CTAs can never
+    // compete for (and block on) the same SM's tensor memory.
+    static_assert(SMEM_BYTES > 116 * 1024 && SMEM_BYTES <= 227 * 1024, "smem budget");
+};
+
+// Dequantize + optional bias for 8 consecutive columns; returns packed halves.
+__device__ __forceinline__ uint4 dequant8(const uint32_t* acc, const half* sn8, const half* bias8, float down_n,
+                                          float batch_scale, bool has_bias, __half& running_absmax) {
+    uint4 ov;
+    half* o = reinterpret_cast<half*>(&ov);
+    const uint4 snv = *reinterpret_cast<const uint4*>(sn8);
+    const half* sn = reinterpret_cast<const half*>(&snv);
+    uint4 bv = make_uint4(0, 0, 0, 0);
+    if (has_bias) bv = *reinterpret_cast<const uint4*>(bias8);
+    const half* b = reinterpret_cast<const half*>(&bv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        // three separately rounded fp32 products in the reference's order, then fp16, then fp16 bias add
+        float t = __fmul_rn((float)(int32_t)acc[j], __half2float(sn[j]));
+        t = __fmul_rn(t, down_n);
+        t = __fmul_rn(t, batch_scale);
+        half h = __float2half_rn(t);
+        if (has_bias) h = __hadd(h, b[j]);
+        o[j] = h;
+        running_absmax = __hmax(running_absmax, __habs(h));
+    }
+    return ov;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const KernelParams p) {
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[C::STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
+    __shared__ __align__(8) uint64_t acc_full_bar[2];
+    __shared__ __align__(8) uint64_t acc_empty_bar[2];
+    __shared__ uint32_t tmem_base_slot;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t ring = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+        for (int s = 0; s < C::STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_addr(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_addr(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_addr(&acc_full_bar[b]), 1);
+            ptx::mbar_init(ptx::smem_addr(&acc_empty_bar[b]), 4);
+        }
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(&tmem_base_slot), C::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles;
+    const int nkb = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int m_tile = tile % p.num_m_tiles;
+                const int n_tile = tile / p.num_m_tiles;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_addr(&empty_bar[stage]), phase ^ 1u, p.status, ST_PRODUCER_TIMEOUT)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = ptx::smem_addr(&full_bar[stage]);
+                    const uint32_t sa = ring + stage * C::STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(full, C::STAGE_BYTES);
+                    ptx::tma_load_2d(sa, &tmap_a, full, kb * BK, m_tile * BM);
+                    ptx::tma_load_2d(sa + C::A_BYTES, &tmap_b, full, kb * BK, n_tile * BN);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_i8_idesc(BM, BN);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+                if (!ptx::mbar_wait(ptx::smem_addr(&acc_empty_bar[buf]), acc_phase ^ 1u, p.status, ST_MMA_ACC_TIMEOUT)) break;
+                ptx::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_addr(&full_bar[stage]), phase, p.status, ST_MMA_FULL_TIMEOUT)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ring + stage * C::STAGE_BYTES;
+                    const uint64_t adesc = ptx::make_kmajor_sw128_desc(sa);
+                    const uint64_t bdesc = ptx::make_kmajor_sw128_desc(sa + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // advancing K inside the 128-byte swizzle row: +32 bytes = +2 in address units of 16 B
+                        ptx::mma_i8(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::mma_commit(ptx::smem_addr(&empty_bar[stage])); // frees the smem slot when these MMAs retire
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::mma_commit(ptx::smem_addr(&acc_full_bar[buf]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue
+        const int quarter = warp & 3; // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
+        const bool has_bias = p.bias != nullptr;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+            const int m_tile = tile % p.num_m_tiles;
+            const int n_tile = tile / p.num_m_tiles;
+            const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+            if (!ptx::mbar_wait(ptx::smem_addr(&acc_full_bar[buf]), acc_phase, p.status, ST_EPI_TIMEOUT)) break;
+            ptx::tc_fence_after();
+
+            const int row = m_tile * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            float batch_scale = 0.0f;
+            if (p.mode != EPI_RAW_I32 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
+            __half absmax = __float2half_rn(0.0f);
+            const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
+
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                const int n0 = n_tile * BN + c0;
+                if (n0 >= p.N) break; // warp-uniform
+                uint32_t acc[32];
+                ptx::tmem_ld_32x32(taddr_row + c0, acc);
+                ptx::tmem_ld_wait();
+                if (!row_ok) continue;
+                if (p.mode == EPI_RAW_I32) {
+                    int32_t* dst = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldc + n0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        if (n0 + j < p.N) // N % 8 == 0, so groups of 4 are all-or-nothing
+                            *reinterpret_cast<uint4*>(dst + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                } else {
+                    half* dst = reinterpret_cast<half*>(p.out) + (int64_t)row * p.ldc + n0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8)
+                        if (n0 + j < p.N)
+                            *reinterpret_cast<uint4*>(dst + j) =
+                                dequant8(acc + j, p.scale_n + n0 + j, p.bias + n0 + j, p.down_n, batch_scale, has_bias, absmax);
+                }
+            }
+            if (p.mode == EPI_DEQUANT_F16_REQUANT_I8 && row_ok)
+                atomicMax(p.row_absmax_bits + row, __float_as_uint(__half2float(absmax)));
+
+            // accumulator buffer drained: hand it back to the MMA warp
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&acc_empty_bar[buf]));
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+// ---- host side ---------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+
+// [rows, K] int8 row-major with leading dimension ld (bytes); box = {128 bytes of K, box_rows}.
+bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+struct DeviceInfo {
+    bool ready = false;
+    int sms = 0;
+    unsigned int* status = nullptr;
+};
+std::mutex g_dev_mutex;
+DeviceInfo g_dev[64];
+
+// One-time set-up for the current device: SM count, the device address of the status word,
+// and the opt-in shared-memory sizes of the kernel instantiations.
+template <int BN> bool set_smem_attr() {
+    return cudaFuncSetAttribute(gemm_i8_tcgen05_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                Cfg<BN>::SMEM_BYTES) == cudaSuccess;
+}
+
+const DeviceInfo* device_info() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceInfo& d = g_dev[dev];
+    if (!d.ready) {
+        if (cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return nullptr;
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_gemm_status) != cudaSuccess) return nullptr;
+        d.status = static_cast<unsigned int*>(addr);
+        if (!set_smem_attr<256>() || !set_smem_attr<128>() || !set_smem_attr<64>() || !set_smem_attr<32>()) return nullptr;
+        d.ready = true;
+    }
+    return &d;
+}
+
+template <int BN>
+int32_t launch_bn(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev) {
+    CUtensorMap ta, tb;
+    if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
+    if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, BN)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
+    KernelParams p;
+    p.M = (int32_t)a.M; p.N = (int32_t)a.N;
+    p.num_m_tiles = (int32_t)((a.M + BM - 1) / BM);
+    p.num_n_tiles = (int32_t)((a.N + BN - 1) / BN);
+    p.num_k_blocks = (int32_t)((a.K + BK - 1) / BK);
+    p.mode = a.mode;
+    p.out = a.out; p.ldc = a.ldc;
+    p.scale_m = a.scale_m; p.scale_n = a.scale_n; p.bias = a.bias;
+    p.down_m = a.down_m; p.down_n = a.down_n;
+    p.row_absmax_bits = a.row_absmax_bits;
+    p.status = dev.status;
+    const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
+    const int grid = (int)(tiles < dev.sms ? tiles : dev.sms);
+    gemm_i8_tcgen05_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);
+    return check_launch("gemm_i8_tcgen05");
+}
+
+} // namespace
+
+int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
+    if (a.M == 0 || a.N == 0) return RC_SUCCESS;
+    const DeviceInfo* dev = device_info();
+    if (!dev) return fail(RC_DEVICE_RUNTIME_ERROR, "device set-up failed: %s", cudaGetErrorString(cudaGetLastError()));
+    if (a.M > INT32_MAX - BM || a.N > INT32_MAX - 256 || a.K > INT32_MAX - BK)
+        return fail(RC_UNSUPPORTED, "GEMM extent beyond 2^31");
+
+    // Tile width: the widest tile that still gives every SM work.
+    const int64_t m_tiles = (a.M + BM - 1) / BM;
+    int bn = 32;
+    const int cand[3] = {256, 128, 64};
+    for (int i = 0; i < 3; ++i) {
+        if (m_tiles * ((a.N + cand[i] - 1) / cand[i]) >= dev->sms) { bn = cand[i]; break; }
+    }
+    switch (bn) {
+    case 256: return launch_bn<256>(stream, a, *dev);
+    case 128: return launch_bn<128>(stream, a, *dev);
+    case 64: return launch_bn<64>(stream, a, *dev);
+    default: return launch_bn<32>(stream, a, *dev);
+    }
+}
+
+int32_t gemm_status(int32_t reset) {
+    const DeviceInfo* dev = device_info();
+    if (!dev) return -1;
+    unsigned int v = 0;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpy(&v, dev->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        unsigned int z = 0;
+        cudaMemcpy(dev->status, &z, sizeof(z), cudaMemcpyHostToDevice);
+    }
+    return (int32_t)v;
+}
+
+} // namespace pplb200

@@ -1,0 +1,299 @@
+// Per-token fp16 -> int8 quantizer, int32 -> fp16 dequantizer and the [w, M, n] -> [M, w, n]
+// transpose of the tensor-parallel gather, for sm_100a.
+//
+// Semantics follow the reference kernels bit for bit:
+//   quantizer   src/ppl/kernel/llm/cuda/pmx/i8i8/quantize.cu:27-80
+//   dequantizer src/ppl/kernel/llm/cuda/pmx/i8i8/quantize.cu:126-169
+// but the quantizer reads each row from HBM once (the row lives in registers between the
+// absmax pass and the rounding pass) instead of twice.
+#include "common.cuh"
+
+namespace pplb200 {
+
+namespace {
+
+constexpr int QTPB = 256;
+
+__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ float block_max(float v, float* red, int nwarps) {
+#pragma unroll
+    for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = red[0];
+    for (int w = 1; w < nwarps; ++w) r = fmaxf(r, red[w]);
+    return r;
+}
+
+// rn(v / scale) as int, identical to (int)__float2int_rn(__fdiv_rn(v, scale)).
+// v * (1/scale) is within a few ulp of the IEEE quotient, so both round to the same integer
+// unless the product sits next to a half-integer; only then is the exact division issued.
+__device__ __forceinline__ int quant_one(float v, float scale, float inv_scale) {
+    const float t = v * inv_scale;
+    const float n = rintf(t);
+    if (fabsf(fabsf(t - n) - 0.5f) < (1.0f / 4096.0f)) return __float2int_rn(__fdiv_rn(v, scale));
+    return __float2int_rn(t);
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+}
+
+// One CTA per row.  A "unit" is 16 consecutive halves (two 128-bit loads, one 128-bit store).
+// Thread t owns units t, t + blockDim.x, ... (UNITS of them), kept in registers.
+template <int UNITS>
+__global__ void __launch_bounds__(QTPB)
+quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, float up_scale, int32_t layout,
+                     int8_t* __restrict__ q, half* __restrict__ scale_out, const uint32_t* __restrict__ given_absmax_bits) {
+    __shared__ float red[QTPB / 32];
+    const int64_t row = blockIdx.x;
+    const int units = (int)(dim >> 4);
+    const uint4* src = reinterpret_cast<const uint4*>(in + row * dim);
+
+    uint4 v[UNITS][2];
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const int unit = u * blockDim.x + threadIdx.x;
+        if (unit < units) {
+            v[u][0] = ldg_stream(src + 2 * unit);
+            v[u][1] = ldg_stream(src + 2 * unit + 1);
+        } else {
+            v[u][0] = make_uint4(0, 0, 0, 0);
+            v[u][1] = make_uint4(0, 0, 0, 0);
+        }
+    }
+
+    float amax;
+    if (given_absmax_bits == nullptr) {
+        // max |x| taken in fp16 (exact: max commutes with the widening conversion); NaNs are dropped
+        // like the reference's fmax chain does.
+        __half2 m2 = __float2half2_rn(0.0f);
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const __half2* h = reinterpret_cast<const __half2*>(&v[u][0]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m2 = __hmax2(m2, __habs2(h[i]));
+        }
+        amax = fmaxf(__low2float(m2), __high2float(m2));
+        amax = block_max(amax, red, blockDim.x >> 5);
+    } else {
+        amax = __uint_as_float(given_absmax_bits[row]);
+    }
+
+    const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-7f);
+    const float inv_scale = __frcp_rn(scale);
+
+#pragma unroll
+    for (int u = 0; u < UNITS; ++u) {
+        const int unit = u * blockDim.x + threadIdx.x;
+        if (unit < units) {
+            const __half2* h = reinterpret_cast<const __half2*>(&v[u][0]);
+            int qi[16];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 f = __half22float2(h[i]);
+                qi[2 * i] = quant_one(f.x, scale, inv_scale);
+                qi[2 * i + 1] = quant_one(f.y, scale, inv_scale);
+            }
+            uint4 o;
+            o.x = pack4(qi[0], qi[1], qi[2], qi[3]);
+            o.y = pack4(qi[4], qi[5], qi[6], qi[7]);
+            o.z = pack4(qi[8], qi[9], qi[10], qi[11]);
+            o.w = pack4(qi[12], qi[13], qi[14], qi[15]);
+            const int64_t off = layout_offset(layout, batch, dim, row, (int64_t)unit << 4);
+            *reinterpret_cast<uint4*>(q + off) = o;
+        }
+    }
+    if (threadIdx.x == 0) scale_out[row] = __float2half_rn(scale * up_scale);
+}
+
+// Rows too long for the register-resident kernel: classic two-pass (second read hits L2 for
+// any realistic row length).
+__global__ void __launch_bounds__(QTPB)
+quantize_rows_twopass_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, float up_scale, int32_t layout,
+                             int8_t* __restrict__ q, half* __restrict__ scale_out,
+                             const uint32_t* __restrict__ given_absmax_bits) {
+    __shared__ float red[QTPB / 32];
+    const int64_t row = blockIdx.x;
+    const int64_t units = dim >> 4;
+    const uint4* src = reinterpret_cast<const uint4*>(in + row * dim);
+    float amax;
+    if (given_absmax_bits == nullptr) {
+        __half2 m2 = __float2half2_rn(0.0f);
+        for (int64_t unit = threadIdx.x; unit < units; unit += blockDim.x) {
+            uint4 a[2] = {src[2 * unit], src[2 * unit + 1]};
+            const __half2* h = reinterpret_cast<const __half2*>(a);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m2 = __hmax2(m2, __habs2(h[i]));
+        }
+        amax = block_max(fmaxf(__low2float(m2), __high2float(m2)), red, blockDim.x >> 5);
+    } else {
+        amax = __uint_as_float(given_absmax_bits[row]);
+    }
+    const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-7f);
+    const float inv_scale = __frcp_rn(scale);
+    for (int64_t unit = threadIdx.x; unit < units; unit += blockDim.x) {
+        uint4 a[2] = {src[2 * unit], src[2 * unit + 1]};
+        const __half2* h = reinterpret_cast<const __half2*>(a);
+        int qi[16];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 f = __half22float2(h[i]);
+            qi[2 * i] = quant_one(f.x, scale, inv_scale);
+            qi[2 * i + 1] = quant_one(f.y, scale, inv_scale);
+        }
+        uint4 o;
+        o.x = pack4(qi[0], qi[1], qi[2], qi[3]);
+        o.y = pack4(qi[4], qi[5], qi[6], qi[7]);
+        o.z = pack4(qi[8], qi[9], qi[10], qi[11]);
+        o.w = pack4(qi[12], qi[13], qi[14], qi[15]);
+        *reinterpret_cast<uint4*>(q + layout_offset(layout, batch, dim, row, unit << 4)) = o;
+    }
+    if (threadIdx.x == 0) scale_out[row] = __float2half_rn(scale * up_scale);
+}
+
+// ---- dequantize ------------------------------------------------------------------------------
+
+__device__ __forceinline__ half dequant_one(int32_t acc, half sn, float down_n, float batch_scale) {
+    // three separately rounded fp32 products, left to right (quantize.cu:157)
+    float t = __fmul_rn((float)acc, __half2float(sn));
+    t = __fmul_rn(t, down_n);
+    t = __fmul_rn(t, batch_scale);
+    return __float2half_rn(t);
+}
+
+// Row-major int32 in, 8 outputs per thread (N % 8 == 0).
+__global__ void __launch_bounds__(256)
+dequantize_rowmajor8_kernel(const int32_t* __restrict__ acc, const half* __restrict__ bias,
+                            const half* __restrict__ scale_m, const half* __restrict__ scale_n,
+                            int64_t batch, int64_t dim, float down_m, float down_n, half* __restrict__ out) {
+    const int64_t chunks_per_row = dim >> 3;
+    const int64_t total = batch * chunks_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / chunks_per_row;
+        const int64_t n = (i - m * chunks_per_row) << 3;
+        const float bs = __fmul_rn(__half2float(scale_m[m]), down_m);
+        const int4 a0 = *reinterpret_cast<const int4*>(acc + m * dim + n);
+        const int4 a1 = *reinterpret_cast<const int4*>(acc + m * dim + n + 4);
+        const uint4 snv = *reinterpret_cast<const uint4*>(scale_n + n);
+        const half* sn = reinterpret_cast<const half*>(&snv);
+        const int32_t a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        uint4 ov;
+        half* o = reinterpret_cast<half*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = dequant_one(a[j], sn[j], down_n, bs);
+        if (bias != nullptr) {
+            const uint4 bv = *reinterpret_cast<const uint4*>(bias + n);
+            const half* b = reinterpret_cast<const half*>(&bv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = __hadd(o[j], b[j]);
+        }
+        *reinterpret_cast<uint4*>(out + m * dim + n) = ov;
+    }
+}
+
+// Any layout / N % 4 == 0: 4 outputs per thread, per-element gather.
+__global__ void __launch_bounds__(256)
+dequantize_generic4_kernel(const int32_t* __restrict__ acc, const half* __restrict__ bias,
+                           const half* __restrict__ scale_m, const half* __restrict__ scale_n,
+                           int64_t batch, int64_t dim, float down_m, float down_n, int32_t layout,
+                           half* __restrict__ out) {
+    const int64_t chunks_per_row = dim >> 2;
+    const int64_t total = batch * chunks_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / chunks_per_row;
+        const int64_t n = (i - m * chunks_per_row) << 2;
+        const float bs = __fmul_rn(__half2float(scale_m[m]), down_m);
+        uint2 ov;
+        half* o = reinterpret_cast<half*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int32_t a = acc[layout_offset(layout, batch, dim, m, n + j)];
+            o[j] = dequant_one(a, scale_n[n + j], down_n, bs);
+            if (bias != nullptr) o[j] = __hadd(o[j], bias[n + j]);
+        }
+        *reinterpret_cast<uint2*>(out + m * dim + n) = ov;
+    }
+}
+
+// [d0, d1, d2] -> [d1, d0, d2] on fp16, 8 halves per thread when d2 % 8 == 0.
+template <typename VEC>
+__global__ void __launch_bounds__(256)
+transpose01_kernel(const VEC* __restrict__ in, int64_t d0, int64_t d1, int64_t d2v, VEC* __restrict__ out) {
+    const int64_t total = d0 * d1 * d2v;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t c = i % d2v, b = (i / d2v) % d1, a = i / (d2v * d1);
+        out[(b * d0 + a) * d2v + c] = in[i];
+    }
+}
+
+int grid_for(int64_t work_items, int tpb) {
+    int64_t blocks = (work_items + tpb - 1) / tpb;
+    const int64_t cap = 148 * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+} // namespace
+
+int32_t launch_quantize(cudaStream_t stream, const half* in, int64_t batch, int64_t dim, float up_scale,
+                        int32_t layout, int8_t* q, half* scale, const uint32_t* given_absmax_bits) {
+    if (batch == 0 || dim == 0) return RC_SUCCESS;
+    const int64_t units = dim >> 4;
+    const unsigned grid = (unsigned)batch;
+    if (units <= QTPB * 8) {
+        // threads: enough to give every thread the same small number of units
+        int per = (int)((units + QTPB - 1) / QTPB);
+        int bucket = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
+        int threads = (int)((units + bucket - 1) / bucket);
+        threads = (threads + 31) / 32 * 32;
+        if (threads > QTPB) threads = QTPB;
+        switch (bucket) {
+        case 1: quantize_rows_kernel<1><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
+        case 2: quantize_rows_kernel<2><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
+        case 4: quantize_rows_kernel<4><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
+        default: quantize_rows_kernel<8><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
+        }
+    } else {
+        quantize_rows_twopass_kernel<<<grid, QTPB, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits);
+    }
+    return check_launch("quantize");
+}
+
+int32_t launch_dequantize(cudaStream_t stream, const int32_t* acc, const half* bias, const half* scale_m,
+                          const half* scale_n, int64_t batch, int64_t dim, float down_m, float down_n,
+                          int32_t layout, half* out) {
+    if (batch == 0 || dim == 0) return RC_SUCCESS;
+    const bool vec8 = layout == LAYOUT_ROW_MAJOR && (dim % 8 == 0) && aligned16(acc) && aligned16(out) &&
+                      aligned16(scale_n) && (bias == nullptr || aligned16(bias));
+    if (vec8) {
+        dequantize_rowmajor8_kernel<<<grid_for(batch * (dim >> 3), 256), 256, 0, stream>>>(
+            acc, bias, scale_m, scale_n, batch, dim, down_m, down_n, out);
+    } else {
+        dequantize_generic4_kernel<<<grid_for(batch * (dim >> 2), 256), 256, 0, stream>>>(
+            acc, bias, scale_m, scale_n, batch, dim, down_m, down_n, layout, out);
+    }
+    return check_launch("dequantize");
+}
+
+int32_t launch_transpose01_f16(cudaStream_t stream, const half* in, int64_t d0, int64_t d1, int64_t d2, half* out) {
+    if (d0 * d1 * d2 == 0) return RC_SUCCESS;
+    if (d2 % 8 == 0 && aligned16(in) && aligned16(out)) {
+        transpose01_kernel<uint4><<<grid_for(d0 * d1 * (d2 >> 3), 256), 256, 0, stream>>>(
+            reinterpret_cast<const uint4*>(in), d0, d1, d2 >> 3, reinterpret_cast<uint4*>(out));
+    } else {
+        transpose01_kernel<uint16_t><<<grid_for(d0 * d1 * d2, 256), 256, 0, stream>>>(
+            reinterpret_cast<const uint16_t*>(in), d0, d1, d2, reinterpret_cast<uint16_t*>(out));
+    }
+    return check_launch("transpose01");
+}
+
+} // namespace pplb200

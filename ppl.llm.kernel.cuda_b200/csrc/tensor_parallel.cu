@@ -1,0 +1,134 @@
+// Tensor-parallel i8i8 linears over NCCL (one process per GPU).
+//   column parallel (N sharded): no communication unless the caller asks for the gathered output
+//   row parallel    (K sharded): int32 partial accumulators are summed across ranks BEFORE the
+//                                dequant epilogue, so the sharded result equals the unsharded one
+//                                bit for bit (integer addition is associative).
+// Reference: src/ppl/kernel/llm/cuda/pmx/i8i8/column_parallel_linear.cu:29-182,
+//            src/ppl/kernel/llm/cuda/pmx/i8i8/row_parallel_linear.cu:28-162.
+#include "common.cuh"
+#include "../../include/pplb200_i8i8.h"
+
+#include <nccl.h>
+
+namespace pplb200 {
+int32_t gemm_entry(cudaStream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N,
+                   int64_t K, int32_t mode, const void* scale_M, const void* scale_N, const void* bias, float down_M,
+                   float down_N, float requant_up, void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q,
+                   void* out_q_scale);
+}
+
+using namespace pplb200;
+
+namespace {
+int32_t nccl_fail(const char* what, ncclResult_t r) {
+    return fail(RC_DEVICE_RUNTIME_ERROR, "%s failed: %s", what, ncclGetErrorString(r));
+}
+bool weight_layout_known(int32_t l) {
+    return l == LAYOUT_ROW_MAJOR || l == LAYOUT_COL4_4R2_8C || l == LAYOUT_COL32_2R_4R4;
+}
+}
+
+extern "C" {
+
+int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream_, const void* input, int64_t M,
+                                            const void* weight, const void* optional_bias,
+                                            const void* scale_M, const void* scale_N,
+                                            float down_scale_M, float down_scale_N,
+                                            int64_t in_features, int64_t out_features, int32_t weight_layout,
+                                            int32_t rank, int32_t size, void* nccl_comm,
+                                            int32_t gather_output, void* gather_buffer, void* quant_buffer,
+                                            void* ws, int64_t ws_bytes, void* output) {
+    (void)quant_buffer;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!weight_layout_known(weight_layout)) return fail(RC_UNSUPPORTED, "unsupported weight layout:%d", weight_layout);
+    // The Turing/Ampere IMMA tile orders (COL4_4R2_8C, COL32_2R_4R4) have no tensor-core path on
+    // sm_100a; weights must be handed over row-major [N/size, K].
+    if (weight_layout != LAYOUT_ROW_MAJOR) return fail(RC_UNSUPPORTED, "weight layout %d is not available on sm_100a; use ROW_MAJOR", weight_layout);
+    if (size < 1 || rank < 0 || rank >= size) return fail(RC_INVALID_VALUE, "bad rank/size %d/%d", rank, size);
+    if (out_features % size) return fail(RC_INVALID_VALUE, "out_features %% size != 0");
+    const int64_t Nw = out_features / size, K = in_features;
+
+    if (!gather_output) // raw int32 accumulators, no dequant (column_parallel_linear.cu:81-85,136)
+        return gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f,
+                          ws, ws_bytes, output, Nw, nullptr, nullptr);
+
+    if (size == 1)
+        return gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_DEQUANT_F16, scale_M, scale_N, optional_bias,
+                          down_scale_M, down_scale_N, 0.f, ws, ws_bytes, output, Nw, nullptr, nullptr);
+
+    if (!gather_buffer || !nccl_comm) return fail(RC_INVALID_VALUE, "gather_output with size > 1 needs gather_buffer and a communicator");
+    half* mine = (half*)gather_buffer + (int64_t)rank * M * Nw;
+    int32_t rc = gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_DEQUANT_F16, scale_M, scale_N, optional_bias,
+                            down_scale_M, down_scale_N, 0.f, ws, ws_bytes, mine, Nw, nullptr, nullptr);
+    if (rc != RC_SUCCESS) return rc;
+    ncclResult_t r = ncclAllGather(mine, gather_buffer, (size_t)(M * Nw), ncclHalf, (ncclComm_t)nccl_comm, stream);
+    if (r != ncclSuccess) return nccl_fail("ncclAllGather", r);
+    return launch_transpose01_f16(stream, (const half*)gather_buffer, size, M, Nw, (half*)output);
+}
+
+int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* input, int64_t M,
+                                         const void* weight, const void* optional_bias,
+                                         const void* scale_M, const void* scale_N,
+                                         float down_scale_M, float down_scale_N,
+                                         int64_t in_features, int64_t out_features, int32_t weight_layout,
+                                         int32_t rank, int32_t size, void* nccl_comm,
+                                         int32_t input_is_parallel, int32_t reduce_mode, void* quant_buffer,
+                                         void* ws, int64_t ws_bytes, void* output) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!input_is_parallel) return fail(RC_UNSUPPORTED, "currently only support parallel input");
+    if (!weight_layout_known(weight_layout)) return fail(RC_UNSUPPORTED, "unsupported weight layout:%d", weight_layout);
+    if (weight_layout != LAYOUT_ROW_MAJOR) return fail(RC_UNSUPPORTED, "weight layout %d is not available on sm_100a; use ROW_MAJOR", weight_layout);
+    if (size < 1 || rank < 0 || rank >= size) return fail(RC_INVALID_VALUE, "bad rank/size %d/%d", rank, size);
+    if (in_features % size) return fail(RC_INVALID_VALUE, "in_features %% size != 0");
+    if (reduce_mode != 0 && reduce_mode != 1) return fail(RC_INVALID_VALUE, "reduce_mode must be 0 or 1");
+    const int64_t N = out_features, Kw = in_features / size;
+
+    if (size == 1)
+        return gemm_entry(stream, input, Kw, weight, Kw, M, N, Kw, EPI_DEQUANT_F16, scale_M, scale_N, optional_bias,
+                          down_scale_M, down_scale_N, 0.f, ws, ws_bytes, output, N, nullptr, nullptr);
+    if (!nccl_comm) return fail(RC_INVALID_VALUE, "size > 1 needs a communicator");
+    if (M == 0 || N == 0) return RC_SUCCESS;
+
+    if (reduce_mode == 1) {
+        // reference order: dequantize the partial (bias on rank 0 only), then sum in fp16
+        const void* reduce_bias = rank == 0 ? optional_bias : nullptr;
+        int32_t rc = gemm_entry(stream, input, Kw, weight, Kw, M, N, Kw, EPI_DEQUANT_F16, scale_M, scale_N, reduce_bias,
+                                down_scale_M, down_scale_N, 0.f, ws, ws_bytes, output, N, nullptr, nullptr);
+        if (rc != RC_SUCCESS) return rc;
+        ncclResult_t r = ncclAllReduce(output, output, (size_t)(M * N), ncclHalf, ncclSum, (ncclComm_t)nccl_comm, stream);
+        return r == ncclSuccess ? RC_SUCCESS : nccl_fail("ncclAllReduce(fp16)", r);
+    }
+
+    if (!quant_buffer) return fail(RC_INVALID_VALUE, "exact row-parallel reduction needs quant_buffer (int32 [M, N])");
+    int32_t rc = gemm_entry(stream, input, Kw, weight, Kw, M, N, Kw, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f,
+                            ws, ws_bytes, quant_buffer, N, nullptr, nullptr);
+    if (rc != RC_SUCCESS) return rc;
+    ncclResult_t r = ncclAllReduce(quant_buffer, quant_buffer, (size_t)(M * N), ncclInt32, ncclSum, (ncclComm_t)nccl_comm, stream);
+    if (r != ncclSuccess) return nccl_fail("ncclAllReduce(int32)", r);
+    return launch_dequantize(stream, (const int32_t*)quant_buffer, (const half*)optional_bias, (const half*)scale_M,
+                             (const half*)scale_N, M, N, down_scale_M, down_scale_N, LAYOUT_ROW_MAJOR, (half*)output);
+}
+
+int32_t pplb200_nccl_get_unique_id(void* id128_host) {
+    static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
+    ncclResult_t r = ncclGetUniqueId((ncclUniqueId*)id128_host);
+    return r == ncclSuccess ? RC_SUCCESS : nccl_fail("ncclGetUniqueId", r);
+}
+
+int32_t pplb200_nccl_comm_init(const void* id128_host, int32_t rank, int32_t size, void** comm_out) {
+    ncclUniqueId id;
+    memcpy(&id, id128_host, sizeof(id));
+    ncclComm_t comm = nullptr;
+    ncclResult_t r = ncclCommInitRank(&comm, size, id, rank);
+    if (r != ncclSuccess) return nccl_fail("ncclCommInitRank", r);
+    *comm_out = comm;
+    return RC_SUCCESS;
+}
+
+int32_t pplb200_nccl_comm_destroy(void* comm) {
+    if (!comm) return RC_SUCCESS;
+    ncclResult_t r = ncclCommDestroy((ncclComm_t)comm);
+    return r == ncclSuccess ? RC_SUCCESS : nccl_fail("ncclCommDestroy", r);
+}
+
+}

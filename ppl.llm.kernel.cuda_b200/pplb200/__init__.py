@@ -1,0 +1,237 @@
+"""Host-side Python binding of the sm_100a i8i8 (W8A8) linear library.
+
+Thin ctypes layer over the C ABI declared in include/pplb200_i8i8.h; function names and
+argument meaning mirror the reference's operator API
+(include/ppl/kernel/llm/cuda/pmx/i8i8/{quantize,column_parallel_linear,row_parallel_linear}.h,
+include/ppl/kernel/llm/cuda/cublas/gemm.h).  torch is used only for device memory and streams.
+
+There is no CPU fallback: importing this module without the built shared library raises.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "..", "lib", "libpplb200_i8i8.so")
+
+# ppl.common RetCode values used by this path
+RC_SUCCESS, RC_UNSUPPORTED, RC_INVALID_VALUE, RC_DEVICE_RUNTIME_ERROR = 0, 2, 4, 10
+
+# matrix_layout_t (common/matrix_layout.h:25-31)
+MATRIX_LAYOUT_ROW_MAJOR, MATRIX_LAYOUT_COL_MAJOR, MATRIX_LAYOUT_COL32 = 0, 1, 2
+MATRIX_LAYOUT_COL32_2R_4R4, MATRIX_LAYOUT_COL4_4R2_8C = 3, 4
+
+EPI_RAW_I32, EPI_DEQUANT_F16, EPI_DEQUANT_F16_REQUANT_I8 = 0, 1, 2
+
+# scale conventions (pmx/i8i8/quantize.h:26-30)
+TOKEN_UP_SCALE, HIDDEN_UP_SCALE = 4096.0, 8192.0
+TOKEN_DOWN_SCALE, HIDDEN_DOWN_SCALE = 1.0 / 4096.0, 1.0 / 8192.0
+
+EXPORTS = [
+    "pplb200_version", "pplb200_last_error",
+    "pplb200_i8i8_minmax_quantize_fp16", "pplb200_i8i8_minmax_dequantize_fp16",
+    "pplb200_i8i8_gemm_workspace_bytes", "pplb200_i8i8_gemm",
+    "pplb200_i8i8_linear_workspace_bytes", "pplb200_i8i8_linear_fp16",
+    "pplb200_i8i8_column_parallel_linear", "pplb200_i8i8_row_parallel_linear",
+    "pplb200_nccl_get_unique_id", "pplb200_nccl_comm_init", "pplb200_nccl_comm_destroy",
+    "pplb200_i8i8_gemm_status", "pplb200_layout_offset",
+]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            "libpplb200_i8i8.so is not built (%s); run `python ppl.llm.kernel.cuda_b200/build.py`. "
+            "There is no fallback path." % os.path.normpath(LIB_PATH))
+    lib = ctypes.CDLL(os.path.normpath(LIB_PATH))
+    vp, i64, i32, f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_float
+    lib.pplb200_version.restype = ctypes.c_char_p
+    lib.pplb200_last_error.restype = ctypes.c_char_p
+    lib.pplb200_i8i8_minmax_quantize_fp16.argtypes = [vp, vp, i64, i64, f32, i32, vp, vp]
+    lib.pplb200_i8i8_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
+    lib.pplb200_i8i8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    lib.pplb200_i8i8_gemm_workspace_bytes.restype = i64
+    lib.pplb200_i8i8_gemm.argtypes = [vp, vp, i64, vp, i64, i64, i64, i64, i32, vp, vp, vp, f32, f32, f32,
+                                      vp, i64, vp, i64, vp, vp]
+    lib.pplb200_i8i8_linear_workspace_bytes.argtypes = [i64, i64, i64, i32]
+    lib.pplb200_i8i8_linear_workspace_bytes.restype = i64
+    lib.pplb200_i8i8_linear_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, f32, f32, f32, i32, f32,
+                                             vp, i64, vp, vp, vp]
+    lib.pplb200_i8i8_column_parallel_linear.argtypes = [vp, vp, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
+                                                        i32, i32, vp, i32, vp, vp, vp, i64, vp]
+    lib.pplb200_i8i8_row_parallel_linear.argtypes = [vp, vp, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
+                                                     i32, i32, vp, i32, i32, vp, vp, i64, vp]
+    lib.pplb200_nccl_get_unique_id.argtypes = [vp]
+    lib.pplb200_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
+    lib.pplb200_nccl_comm_destroy.argtypes = [vp]
+    lib.pplb200_i8i8_gemm_status.argtypes = [i32]
+    lib.pplb200_layout_offset.argtypes = [i32, i64, i64, i64, i64]
+    lib.pplb200_layout_offset.restype = i64
+    for name in EXPORTS:
+        fn = getattr(lib, name)
+        if fn.restype is ctypes.c_int:
+            fn.restype = i32
+    return lib
+
+
+lib = _load()
+
+
+class PplError(RuntimeError):
+    def __init__(self, rc):
+        self.rc = rc
+        super().__init__("pplb200 call failed: RetCode %d: %s" % (rc, last_error()))
+
+
+def version():
+    return lib.pplb200_version().decode()
+
+
+def last_error():
+    return lib.pplb200_last_error().decode()
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(rc):
+    if rc != RC_SUCCESS:
+        raise PplError(rc)
+
+
+def minmax_quantize_fp16(x, up_scale=TOKEN_UP_SCALE, to_layout=MATRIX_LAYOUT_ROW_MAJOR, out=None, scale=None):
+    """x fp16 [batch, dim] (cuda) -> (q int8 [batch, dim] in `to_layout`, scale fp16 [batch])."""
+    import torch
+    batch, dim = x.shape
+    q = out if out is not None else torch.empty((batch, dim), dtype=torch.int8, device=x.device)
+    s = scale if scale is not None else torch.empty((batch,), dtype=torch.float16, device=x.device)
+    _check(lib.pplb200_i8i8_minmax_quantize_fp16(_stream(), _ptr(x), batch, dim, up_scale, to_layout, _ptr(q), _ptr(s)))
+    return q, s
+
+
+def minmax_dequantize_fp16(acc, scale_m, scale_n, bias=None, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE,
+                           from_layout=MATRIX_LAYOUT_ROW_MAJOR, out=None, shape=None):
+    import torch
+    batch, dim = shape if shape is not None else acc.shape
+    y = out if out is not None else torch.empty((batch, dim), dtype=torch.float16, device=acc.device)
+    _check(lib.pplb200_i8i8_minmax_dequantize_fp16(_stream(), _ptr(acc), _ptr(bias), _ptr(scale_m), _ptr(scale_n),
+                                                   batch, dim, down_m, down_n, from_layout, _ptr(y)))
+    return y
+
+
+def gemm_workspace_bytes(M, N, K, mode):
+    return lib.pplb200_i8i8_gemm_workspace_bytes(M, N, K, mode)
+
+
+def gemm_i8i8(a, b, mode=EPI_RAW_I32, scale_m=None, scale_n=None, bias=None, down_m=TOKEN_DOWN_SCALE,
+              down_n=HIDDEN_DOWN_SCALE, requant_up_scale=TOKEN_UP_SCALE, ws=None, out=None):
+    """a int8 [M,K], b int8 [N,K] -> int32 [M,N] (mode 0) / fp16 [M,N] (mode 1) / (fp16, int8, fp16 scales) (mode 2)."""
+    import torch
+    M, K = a.shape
+    N = b.shape[0]
+    dt = torch.int32 if mode == EPI_RAW_I32 else torch.float16
+    y = out if out is not None else torch.empty((M, N), dtype=dt, device=a.device)
+    yq = ys = None
+    need = gemm_workspace_bytes(M, N, K, mode)
+    if need and ws is None:
+        ws = torch.empty((need,), dtype=torch.uint8, device=a.device)
+    if mode == EPI_DEQUANT_F16_REQUANT_I8:
+        yq = torch.empty((M, N), dtype=torch.int8, device=a.device)
+        ys = torch.empty((M,), dtype=torch.float16, device=a.device)
+    _check(lib.pplb200_i8i8_gemm(_stream(), _ptr(a), a.stride(0), _ptr(b), b.stride(0), M, N, K, mode, _ptr(scale_m),
+                                 _ptr(scale_n), _ptr(bias), down_m, down_n, requant_up_scale, _ptr(ws),
+                                 0 if ws is None else ws.numel(), _ptr(y), y.stride(0), _ptr(yq), _ptr(ys)))
+    return y if mode != EPI_DEQUANT_F16_REQUANT_I8 else (y, yq, ys)
+
+
+def linear_workspace_bytes(M, N, K, mode):
+    return lib.pplb200_i8i8_linear_workspace_bytes(M, N, K, mode)
+
+
+class W8A8Linear:
+    """Pre-allocated single-device W8A8 linear: y = dequant(quantize(x) @ W^T) (+bias) [-> re-quantize].
+
+    Owns the outputs and workspace so that __call__ allocates nothing (the C ABI never does)."""
+
+    def __init__(self, w, scale_n, bias=None, max_tokens=None, requant=False):
+        import torch
+        self.w, self.scale_n, self.bias = w, scale_n, bias
+        self.N, self.K = w.shape
+        self.max_tokens = max_tokens
+        self.mode = EPI_DEQUANT_F16_REQUANT_I8 if requant else EPI_DEQUANT_F16
+        dev = w.device
+        self.ws = torch.empty((linear_workspace_bytes(max_tokens, self.N, self.K, self.mode),), dtype=torch.uint8, device=dev)
+        self.y = torch.empty((max_tokens, self.N), dtype=torch.float16, device=dev)
+        self.yq = torch.empty((max_tokens, self.N), dtype=torch.int8, device=dev) if requant else None
+        self.ys = torch.empty((max_tokens,), dtype=torch.float16, device=dev) if requant else None
+
+    def __call__(self, x):
+        M = x.shape[0]
+        assert M <= self.max_tokens and x.shape[1] == self.K
+        _check(lib.pplb200_i8i8_linear_fp16(_stream(), _ptr(x), _ptr(self.w), _ptr(self.scale_n), _ptr(self.bias),
+                                            M, self.N, self.K, TOKEN_UP_SCALE, TOKEN_DOWN_SCALE, HIDDEN_DOWN_SCALE,
+                                            self.mode, TOKEN_UP_SCALE, _ptr(self.ws), self.ws.numel(),
+                                            _ptr(self.y), _ptr(self.yq), _ptr(self.ys)))
+        if self.yq is None:
+            return self.y[:M]
+        return self.y[:M], self.yq[:M], self.ys[:M]
+
+
+def column_parallel_linear(xq, w, scale_m, scale_n, bias, in_features, out_features, rank=0, size=1, comm=None,
+                           gather_output=True, gather_buffer=None, out=None, down_m=TOKEN_DOWN_SCALE,
+                           down_n=HIDDEN_DOWN_SCALE, weight_layout=MATRIX_LAYOUT_ROW_MAJOR):
+    import torch
+    M = xq.shape[0]
+    Nw = out_features // size
+    if out is None:
+        if gather_output:
+            out = torch.empty((M, out_features), dtype=torch.float16, device=xq.device)
+        else:
+            out = torch.empty((M, Nw), dtype=torch.int32, device=xq.device)
+    _check(lib.pplb200_i8i8_column_parallel_linear(_stream(), _ptr(xq), M, _ptr(w), _ptr(bias), _ptr(scale_m),
+                                                   _ptr(scale_n), down_m, down_n, in_features, out_features,
+                                                   weight_layout, rank, size, comm, 1 if gather_output else 0,
+                                                   _ptr(gather_buffer), None, None, 0, _ptr(out)))
+    return out
+
+
+def row_parallel_linear(xq, w, scale_m, scale_n, bias, in_features, out_features, rank=0, size=1, comm=None,
+                        input_is_parallel=True, reduce_mode=0, quant_buffer=None, out=None,
+                        down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE, weight_layout=MATRIX_LAYOUT_ROW_MAJOR):
+    import torch
+    M = xq.shape[0]
+    if out is None:
+        out = torch.empty((M, out_features), dtype=torch.float16, device=xq.device)
+    if quant_buffer is None and size > 1 and reduce_mode == 0:
+        quant_buffer = torch.empty((M, out_features), dtype=torch.int32, device=xq.device)
+    _check(lib.pplb200_i8i8_row_parallel_linear(_stream(), _ptr(xq), M, _ptr(w), _ptr(bias), _ptr(scale_m),
+                                                _ptr(scale_n), down_m, down_n, in_features, out_features,
+                                                weight_layout, rank, size, comm, 1 if input_is_parallel else 0,
+                                                reduce_mode, _ptr(quant_buffer), None, 0, _ptr(out)))
+    return out
+
+
+def gemm_status(reset=True):
+    return lib.pplb200_i8i8_gemm_status(1 if reset else 0)
+
+
+def nccl_unique_id():
+    buf = ctypes.create_string_buffer(128)
+    _check(lib.pplb200_nccl_get_unique_id(buf))
+    return bytes(buf.raw)
+
+
+def nccl_comm_init(uid, rank, size):
+    comm = ctypes.c_void_p()
+    buf = ctypes.create_string_buffer(uid, 128)
+    _check(lib.pplb200_nccl_comm_init(buf, rank, size, ctypes.byref(comm)))
+    return comm
+
+
+def nccl_comm_destroy(comm):
+    _check(lib.pplb200_nccl_comm_destroy(comm))
