@@ -1,0 +1,54 @@
+// Per-token quantize / dequantize operators with the reference's names, argument order and
+// scale conventions (include/ppl/kernel/llm/cuda/pmx/i8i8/quantize.h:26-55), forwarded to the
+// sm_100a kernels through the C ABI.
+#ifndef PPLB200_PPL_KERNEL_LLM_CUDA_PMX_I8I8_QUANTIZE_H
+#define PPLB200_PPL_KERNEL_LLM_CUDA_PMX_I8I8_QUANTIZE_H
+
+#include "ppl/kernel/llm/cuda/common/general_include.h"
+#include "ppl/kernel/llm/cuda/common/matrix_layout.h"
+#include "pplb200_i8i8.h"
+
+namespace ppl { namespace kernel { namespace llm { namespace cuda { namespace pmx { namespace i8i8 {
+
+// fp16 scale vectors store scale * up_scale so that small scales stay clear of fp16 subnormals;
+// the dequantizer multiplies by the matching down scale.
+constexpr float token_up_scale = 4096.0f;
+constexpr float hidden_up_scale = 8192.0f;
+constexpr float token_down_scale = 1.0f / 4096.0f;
+constexpr float hidden_down_scale = 1.0f / 8192.0f;
+
+inline ppl::common::RetCode minmax_quantize_fp16(
+    cudaStream_t stream,
+    const void* input,           // fp16, [batch, quant_dim]
+    const int64_t batch,
+    const int64_t quant_dim,
+    const float up_scale,        // scale[i] = scale_val * up_scale
+    const matrix_layout_t to_layout,
+    void* quantized,             // int8, [batch, quant_dim]
+    void* scale)                 // fp16, [batch]
+{
+    return (ppl::common::RetCode)pplb200_i8i8_minmax_quantize_fp16(
+        (pplb200_stream_t)stream, input, batch, quant_dim, up_scale, (int32_t)to_layout, quantized, scale);
+}
+
+inline ppl::common::RetCode minmax_dequantize_fp16(
+    cudaStream_t stream,
+    const void* input,              // int32, [batch, quant_dim] in from_layout
+    const void* optional_bias,      // fp16, [quant_dim]
+    const void* scale_per_batch,    // fp16, [batch]
+    const void* scale_per_channel,  // fp16, [quant_dim]
+    const int64_t batch,
+    const int64_t quant_dim,
+    const float down_scale_batch,
+    const float down_scale_channel,
+    const matrix_layout_t from_layout,
+    void* output)                   // fp16, [batch, quant_dim]
+{
+    return (ppl::common::RetCode)pplb200_i8i8_minmax_dequantize_fp16(
+        (pplb200_stream_t)stream, input, optional_bias, scale_per_batch, scale_per_channel, batch, quant_dim,
+        down_scale_batch, down_scale_channel, (int32_t)from_layout, output);
+}
+
+}}}}}}
+
+#endif
