@@ -46,7 +46,7 @@ def build(force=False, verbose=False):
                 print(" ".join(cmd))
             subprocess.run(cmd, check=True)
     if force or _stale(LIB, objs):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lnccl"]
+        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-ldl"]
         if verbose:
             print(" ".join(cmd))
         subprocess.run(cmd, check=True)

@@ -8,7 +8,49 @@
 #include "common.cuh"
 #include "../../include/pplb200_i8i8.h"
 
+#include <dlfcn.h>
+#include <mutex>
 #include <nccl.h>
+#include <string.h>
+
+// NCCL is bound at first use instead of at link time: a process that already carries an NCCL
+// (for instance the one bundled with its deep-learning framework) keeps using that single copy,
+// whatever the import order; otherwise the system libnccl.so.2 is loaded.
+namespace {
+struct NcclApi {
+    bool ok = false;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*AllReduce)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*ReduceScatter)(const void*, void*, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+};
+
+const NcclApi& nccl_api() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return;
+#define PPLB200_BIND(field, name) api.field = reinterpret_cast<decltype(api.field)>(dlsym(h, name))
+        PPLB200_BIND(GetUniqueId, "ncclGetUniqueId");
+        PPLB200_BIND(CommInitRank, "ncclCommInitRank");
+        PPLB200_BIND(CommDestroy, "ncclCommDestroy");
+        PPLB200_BIND(AllReduce, "ncclAllReduce");
+        PPLB200_BIND(AllGather, "ncclAllGather");
+        PPLB200_BIND(ReduceScatter, "ncclReduceScatter");
+        PPLB200_BIND(GetErrorString, "ncclGetErrorString");
+#undef PPLB200_BIND
+        api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.AllGather &&
+                 api.ReduceScatter && api.GetErrorString;
+    });
+    return api;
+}
+}
 
 namespace pplb200 {
 int32_t gemm_entry(cudaStream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N,
@@ -21,8 +63,9 @@ using namespace pplb200;
 
 namespace {
 int32_t nccl_fail(const char* what, ncclResult_t r) {
-    return fail(RC_DEVICE_RUNTIME_ERROR, "%s failed: %s", what, ncclGetErrorString(r));
+    return fail(RC_DEVICE_RUNTIME_ERROR, "%s failed: %s", what, nccl_api().ok ? nccl_api().GetErrorString(r) : "NCCL not loaded");
 }
+int32_t nccl_missing() { return fail(RC_DEVICE_RUNTIME_ERROR, "libnccl.so.2 could not be loaded"); }
 bool weight_layout_known(int32_t l) {
     return l == LAYOUT_ROW_MAJOR || l == LAYOUT_COL4_4R2_8C || l == LAYOUT_COL32_2R_4R4;
 }
@@ -57,11 +100,12 @@ int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream_, const void
                           down_scale_M, down_scale_N, 0.f, ws, ws_bytes, output, Nw, nullptr, nullptr);
 
     if (!gather_buffer || !nccl_comm) return fail(RC_INVALID_VALUE, "gather_output with size > 1 needs gather_buffer and a communicator");
+    if (!nccl_api().ok) return nccl_missing();
     half* mine = (half*)gather_buffer + (int64_t)rank * M * Nw;
     int32_t rc = gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_DEQUANT_F16, scale_M, scale_N, optional_bias,
                             down_scale_M, down_scale_N, 0.f, ws, ws_bytes, mine, Nw, nullptr, nullptr);
     if (rc != RC_SUCCESS) return rc;
-    ncclResult_t r = ncclAllGather(mine, gather_buffer, (size_t)(M * Nw), ncclHalf, (ncclComm_t)nccl_comm, stream);
+    ncclResult_t r = nccl_api().AllGather(mine, gather_buffer, (size_t)(M * Nw), ncclHalf, (ncclComm_t)nccl_comm, stream);
     if (r != ncclSuccess) return nccl_fail("ncclAllGather", r);
     return launch_transpose01_f16(stream, (const half*)gather_buffer, size, M, Nw, (half*)output);
 }
@@ -87,6 +131,7 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* i
         return gemm_entry(stream, input, Kw, weight, Kw, M, N, Kw, EPI_DEQUANT_F16, scale_M, scale_N, optional_bias,
                           down_scale_M, down_scale_N, 0.f, ws, ws_bytes, output, N, nullptr, nullptr);
     if (!nccl_comm) return fail(RC_INVALID_VALUE, "size > 1 needs a communicator");
+    if (!nccl_api().ok) return nccl_missing();
     if (M == 0 || N == 0) return RC_SUCCESS;
 
     if (reduce_mode == 1) {
@@ -95,7 +140,7 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* i
         int32_t rc = gemm_entry(stream, input, Kw, weight, Kw, M, N, Kw, EPI_DEQUANT_F16, scale_M, scale_N, reduce_bias,
                                 down_scale_M, down_scale_N, 0.f, ws, ws_bytes, output, N, nullptr, nullptr);
         if (rc != RC_SUCCESS) return rc;
-        ncclResult_t r = ncclAllReduce(output, output, (size_t)(M * N), ncclHalf, ncclSum, (ncclComm_t)nccl_comm, stream);
+        ncclResult_t r = nccl_api().AllReduce(output, output, (size_t)(M * N), ncclHalf, ncclSum, (ncclComm_t)nccl_comm, stream);
         return r == ncclSuccess ? RC_SUCCESS : nccl_fail("ncclAllReduce(fp16)", r);
     }
 
@@ -103,7 +148,7 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* i
     int32_t rc = gemm_entry(stream, input, Kw, weight, Kw, M, N, Kw, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f,
                             ws, ws_bytes, quant_buffer, N, nullptr, nullptr);
     if (rc != RC_SUCCESS) return rc;
-    ncclResult_t r = ncclAllReduce(quant_buffer, quant_buffer, (size_t)(M * N), ncclInt32, ncclSum, (ncclComm_t)nccl_comm, stream);
+    ncclResult_t r = nccl_api().AllReduce(quant_buffer, quant_buffer, (size_t)(M * N), ncclInt32, ncclSum, (ncclComm_t)nccl_comm, stream);
     if (r != ncclSuccess) return nccl_fail("ncclAllReduce(int32)", r);
     return launch_dequantize(stream, (const int32_t*)quant_buffer, (const half*)optional_bias, (const half*)scale_M,
                              (const half*)scale_N, M, N, down_scale_M, down_scale_N, LAYOUT_ROW_MAJOR, (half*)output);
@@ -111,15 +156,17 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* i
 
 int32_t pplb200_nccl_get_unique_id(void* id128_host) {
     static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
-    ncclResult_t r = ncclGetUniqueId((ncclUniqueId*)id128_host);
+    if (!nccl_api().ok) return nccl_missing();
+    ncclResult_t r = nccl_api().GetUniqueId((ncclUniqueId*)id128_host);
     return r == ncclSuccess ? RC_SUCCESS : nccl_fail("ncclGetUniqueId", r);
 }
 
 int32_t pplb200_nccl_comm_init(const void* id128_host, int32_t rank, int32_t size, void** comm_out) {
+    if (!nccl_api().ok) return nccl_missing();
     ncclUniqueId id;
     memcpy(&id, id128_host, sizeof(id));
     ncclComm_t comm = nullptr;
-    ncclResult_t r = ncclCommInitRank(&comm, size, id, rank);
+    ncclResult_t r = nccl_api().CommInitRank(&comm, size, id, rank);
     if (r != ncclSuccess) return nccl_fail("ncclCommInitRank", r);
     *comm_out = comm;
     return RC_SUCCESS;
@@ -127,7 +174,8 @@ int32_t pplb200_nccl_comm_init(const void* id128_host, int32_t rank, int32_t siz
 
 int32_t pplb200_nccl_comm_destroy(void* comm) {
     if (!comm) return RC_SUCCESS;
-    ncclResult_t r = ncclCommDestroy((ncclComm_t)comm);
+    if (!nccl_api().ok) return nccl_missing();
+    ncclResult_t r = nccl_api().CommDestroy((ncclComm_t)comm);
     return r == ncclSuccess ? RC_SUCCESS : nccl_fail("ncclCommDestroy", r);
 }
 
