@@ -1,0 +1,120 @@
+"""GPU-less checks of the product's boundary: the shared library loads, exports every symbol the
+C header declares, its host-only helpers agree with the oracle, and the reference-compatible C++
+headers compile against the stand-in ppl.common headers."""
+import os
+import re
+import subprocess
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "pplb200_i8i8.h")
+
+
+def declared_symbols():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(pplb200_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_library_exports_every_declared_symbol():
+    import pplb200
+    names = declared_symbols()
+    assert len(names) >= 14
+    for n in names:
+        assert hasattr(pplb200.lib, n), "missing export: " + n
+    assert set(names) == set(pplb200.EXPORTS)
+    assert "sm_100a" in pplb200.version()
+
+
+def test_no_torch_types_in_c_header():
+    src = open(HEADER).read()
+    assert "torch" not in src.lower() and "at::" not in src and "#include <cuda" not in src
+
+
+@pytest.mark.parametrize("layout", [0, 1, 2, 3, 4])
+def test_layout_offsets_match_oracle(oracle, layout):
+    import pplb200
+    rows, cols = 64, 96
+    for r in range(rows):
+        for c in range(0, cols, 5):
+            assert pplb200.lib.pplb200_layout_offset(layout, rows, cols, r, c) == oracle.layout_offset(layout, rows, cols, r, c)
+    assert pplb200.lib.pplb200_layout_offset(9, rows, cols, 0, 0) == -1
+
+
+def test_workspace_sizes():
+    import pplb200
+    assert pplb200.gemm_workspace_bytes(128, 12288, 4096, pplb200.EPI_RAW_I32) == 0
+    assert pplb200.gemm_workspace_bytes(128, 12288, 4096, pplb200.EPI_DEQUANT_F16) == 0
+    assert pplb200.gemm_workspace_bytes(128, 12288, 4096, pplb200.EPI_DEQUANT_F16_REQUANT_I8) >= 128 * 4
+    need = pplb200.linear_workspace_bytes(128, 12288, 4096, pplb200.EPI_DEQUANT_F16_REQUANT_I8)
+    assert need >= 128 * 4096 + 128 * 2 + 128 * 4 and need % 256 == 0
+
+
+def test_reference_compatible_headers_compile(tmp_path):
+    """A translation unit written against the reference's operator API (same namespaces, names and
+    argument lists as its own call sites) compiles unchanged against include/."""
+    src = tmp_path / "caller.cpp"
+    src.write_text(r'''
+#include "ppl/kernel/llm/cuda/pmx/i8i8/quantize.h"
+#include "ppl/kernel/llm/cuda/pmx/i8i8/column_parallel_linear.h"
+#include "ppl/kernel/llm/cuda/pmx/i8i8/row_parallel_linear.h"
+#include "ppl/kernel/llm/cuda/cublas/gemm.h"
+namespace k = ppl::kernel::llm::cuda;
+ppl::common::RetCode run(cudaStream_t s, cublasLtHandle_t lt, k::cublas::AlgoCache* cache, ppl::common::NcclParam* nccl,
+                         const void* x, void* xq, void* sm, const void* w, const void* sn, const void* bias,
+                         void* qbuf, void* ws, void* y) {
+    ppl::common::TensorShape in(ppl::common::DATATYPE_INT8, {2, 8, 4096}), wt(ppl::common::DATATYPE_INT8, {4096, 4096});
+    ppl::common::TensorShape b(ppl::common::DATATYPE_FLOAT16, {4096}), out(ppl::common::DATATYPE_FLOAT16, {2, 8, 4096});
+    auto rc = k::pmx::i8i8::minmax_quantize_fp16(s, x, 16, 4096, k::pmx::i8i8::token_up_scale, k::MATRIX_LAYOUT_ROW_MAJOR, xq, sm);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    rc = k::pmx::i8i8::column_parallel_linear(s, lt, nullptr, &in, xq, &wt, w, &b, bias, sm, sn,
+        k::pmx::i8i8::token_down_scale, k::pmx::i8i8::hidden_down_scale, 4096, 4096, k::MATRIX_LAYOUT_ROW_MAJOR,
+        nccl, true, nullptr, qbuf, 0, ws, cache, &out, y);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    rc = k::pmx::i8i8::row_parallel_linear(s, lt, nullptr, &in, xq, &wt, w, &b, bias, sm, sn,
+        k::pmx::i8i8::token_down_scale, k::pmx::i8i8::hidden_down_scale, 4096, 4096, k::MATRIX_LAYOUT_ROW_MAJOR,
+        nccl, true, nullptr, qbuf, 0, ws, cache, &out, y);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    rc = k::cublas::gemm_i8i8i32(s, lt, nullptr, false, 4096, ppl::common::DATATYPE_INT8, xq, true, 4096,
+        ppl::common::DATATYPE_INT8, w, nullptr, 16, 4096, 4096, 1, 0, 0, ws, cache, 4096, ppl::common::DATATYPE_INT32, qbuf);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    return k::pmx::i8i8::minmax_dequantize_fp16(s, qbuf, bias, sm, sn, 16, 4096, k::pmx::i8i8::token_down_scale,
+        k::pmx::i8i8::hidden_down_scale, k::MATRIX_LAYOUT_ROW_MAJOR, y);
+}
+int main() {
+    k::MatrixLayoutHelper<k::MATRIX_LAYOUT_COL32> h;
+    h.Init(4, 64);
+    return h.GetOffset(1, 33) == 4 * 32 + 32 + 1 ? 0 : 1;
+}
+''')
+    exe = tmp_path / "caller"
+    cmd = ["g++", "-std=c++17", "-Wall", "-Werror", "-I" + os.path.join(ROOT, "include"),
+           "-I" + os.path.join(ROOT, "include", "compat"), "-I/usr/local/cuda/include", str(src), "-o", str(exe),
+           "-L" + os.path.join(ROOT, "ppl.llm.kernel.cuda_b200", "lib"), "-lpplb200_i8i8",
+           "-Wl,-rpath," + os.path.join(ROOT, "ppl.llm.kernel.cuda_b200", "lib")]
+    subprocess.run(cmd, check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
+
+
+def test_workload_generators_are_deterministic_and_shaped():
+    from pplb200 import workloads as wl
+    assert [wl.algorithmic_bytes(n) for n in ("c0", "c1", "c2", "c3", "c4")] == \
+        [17055744, 56148224, 304131072, 385908736, 838918144]
+    x1, x2 = wl.make_activations("c2", 40), wl.make_activations("c2", 300)
+    assert x1.dtype == np.float16 and x1.shape == (40, 4096) and np.array_equal(x1, x2[:40])
+    ch = wl.outlier_channels("c2")
+    assert len(ch) == 40 and len(np.unique(ch)) == 40
+    col_rms = np.sqrt((x2.astype(np.float32) ** 2).mean(axis=0))
+    assert col_rms[ch].min() > 20 and np.delete(col_rms, ch).max() < 2
+    x4 = wl.make_activations("c4", 64).astype(np.float32)
+    assert np.abs(x4).max() <= 200 and np.abs(x4).max() > 20      # heavy tails, clipped
+    w = wl.make_weights("c0")
+    assert w.dtype == np.int8 and w.min() == -127 and w.max() == 127
+    s = wl.make_column_scales("c3").astype(np.float32) / 8192
+    assert 0.0005 * 0.999 <= s.min() and s.max() <= 0.005 * 1.001
+    assert wl.make_bias("c2") is None and wl.make_bias("c0").shape == (4096,)
+    assert wl.shard_rows(22016, 8, 7) == (19264, 22016)
+    with pytest.raises(AssertionError):
+        wl.shard_rows(10, 4, 0)

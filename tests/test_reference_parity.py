@@ -1,0 +1,178 @@
+"""Pins the oracle (and the CUDA path) against the reference's OWN kernels, compiled unmodified
+from the reference tree into oracle/_ref/libref_i8i8.so and run on this GPU.
+
+The reference has no golden vectors for this path, so this is the anchor of every parity claim:
+    reference kernels == oracle   (int8 / int32 / scales bit-exact, fp16 <= 1 ulp, 0 expected)
+    reference kernels == this library, same bar.
+Skipped (not failed) when oracle/_ref was not built -- it needs the reference tree at build time."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_SO = os.path.join(ROOT, "oracle", "_ref", "libref_i8i8.so")
+
+
+@pytest.fixture(scope="module")
+def ref(cuda):
+    if not os.path.exists(REF_SO):
+        pytest.skip("oracle/_ref/libref_i8i8.so not built (reference tree absent at build time)")
+    lib = ctypes.CDLL(REF_SO)
+    vp, i64, i32, f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_float
+    lib.ref_minmax_quantize_fp16.argtypes = [vp, vp, i64, i64, f32, i32, vp, vp]
+    lib.ref_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
+    lib.ref_gemm_i8i8i32.argtypes = [vp, vp, vp, i64, i64, i64, vp, i64, vp]
+    lib.ref_column_parallel_linear.argtypes = [vp, vp, vp, vp, vp, vp, f32, f32, i64, i64, i64, i32, vp, vp, i64, vp]
+    return lib
+
+
+def _t(torch, a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _x(rng, M, K, kind):
+    if kind == "normal":
+        x = rng.standard_normal((M, K))
+    elif kind == "outlier":
+        x = rng.standard_normal((M, K))
+        x[:, rng.choice(K, K // 100, replace=False)] *= 50
+    elif kind == "ties":
+        x = rng.integers(-254, 255, (M, K)) / 2.0
+        x[:, 0] = 127.0
+    elif kind == "tiny":
+        x = rng.standard_normal((M, K)) * 1e-6
+    else:
+        raise ValueError(kind)
+    return x.astype(np.float16)
+
+
+@pytest.mark.parametrize("M,K", [(16, 4096), (128, 4096), (5, 28672), (40, 512)])
+@pytest.mark.parametrize("kind", ["normal", "outlier", "ties", "tiny"])
+def test_quantizer_three_way(cuda, oracle, ref, M, K, kind):
+    import pplb200
+    rng = np.random.default_rng(M + K)
+    x = _x(rng, M, K, kind)
+    tx = _t(cuda, x)
+    q_r = cuda.empty((M, K), dtype=cuda.int8, device="cuda")
+    s_r = cuda.empty((M,), dtype=cuda.float16, device="cuda")
+    assert ref.ref_minmax_quantize_fp16(None, _p(tx), M, K, 4096.0, 0, _p(q_r), _p(s_r)) == 0
+    q_o, s_o = oracle.quantize(x)[1:]
+    q_m, s_m = pplb200.minmax_quantize_fp16(tx)
+    cuda.cuda.synchronize()
+    assert np.array_equal(q_r.cpu().numpy(), q_o), "reference kernel vs oracle: int8"
+    assert np.array_equal(oracle.f16_bits(s_r.cpu().numpy()), oracle.f16_bits(s_o)), "reference kernel vs oracle: scales"
+    assert cuda.equal(q_r, q_m) and cuda.equal(s_r.view(cuda.int16), s_m.view(cuda.int16)), "reference kernel vs library"
+
+
+@pytest.mark.parametrize("layout", [2, 3])
+def test_quantizer_col32_three_way(cuda, oracle, ref, layout):
+    import pplb200
+    rng = np.random.default_rng(layout)
+    M, K = 64, 256
+    x = _x(rng, M, K, "normal")
+    tx = _t(cuda, x)
+    q_r = cuda.zeros((M, K), dtype=cuda.int8, device="cuda")
+    s_r = cuda.empty((M,), dtype=cuda.float16, device="cuda")
+    assert ref.ref_minmax_quantize_fp16(None, _p(tx), M, K, 4096.0, layout, _p(q_r), _p(s_r)) == 0
+    q_o = oracle.quantize(x, layout=layout)[1]
+    q_m, _ = pplb200.minmax_quantize_fp16(tx, to_layout=layout)
+    assert np.array_equal(q_r.cpu().numpy(), q_o)
+    assert cuda.equal(q_r, q_m)
+
+
+@pytest.mark.parametrize("M,N", [(16, 4096), (128, 12288), (33, 1000)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_dequantizer_three_way(cuda, oracle, ref, M, N, with_bias):
+    import pplb200
+    rng = np.random.default_rng(M * 3 + N)
+    acc = rng.integers(-(2 ** 28), 2 ** 28, (M, N), dtype=np.int32)
+    sm = (rng.uniform(0.001, 2.0, M) * 4096 / 127).astype(np.float16)
+    sn = (rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float16) if with_bias else None
+    ta, tsm, tsn = _t(cuda, acc), _t(cuda, sm), _t(cuda, sn)
+    tb = None if bias is None else _t(cuda, bias)
+    y_r = cuda.empty((M, N), dtype=cuda.float16, device="cuda")
+    assert ref.ref_minmax_dequantize_fp16(None, _p(ta), _p(tb), _p(tsm), _p(tsn), M, N, 1 / 4096, 1 / 8192, 0, _p(y_r)) == 0
+    y_o = oracle.dequantize(acc, sm, sn, bias)[1]
+    y_m = pplb200.minmax_dequantize_fp16(ta, tsm, tsn, tb)
+    cuda.cuda.synchronize()
+    assert oracle.ulp_diff_f16(y_r.cpu().numpy(), y_o).max() == 0, "reference kernel vs oracle"
+    assert cuda.equal(y_r.view(cuda.int16), y_m.view(cuda.int16)), "reference kernel vs library"
+
+
+@pytest.mark.parametrize("layout", [2, 3, 4])
+def test_dequantizer_layouts_vs_reference(cuda, oracle, ref, layout):
+    rng = np.random.default_rng(layout + 10)
+    M, N = 64, 128
+    acc = rng.integers(-(2 ** 20), 2 ** 20, (M, N), dtype=np.int32)
+    flat, _ = oracle.to_layout(acc, layout)
+    sm = (rng.uniform(0.01, 2.0, M) * 4096 / 127).astype(np.float16)
+    sn = (rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)
+    y_r = cuda.empty((M, N), dtype=cuda.float16, device="cuda")
+    t_flat, t_sm, t_sn = _t(cuda, flat), _t(cuda, sm), _t(cuda, sn)  # named: must outlive the asynchronous launch
+    assert ref.ref_minmax_dequantize_fp16(None, _p(t_flat), None, _p(t_sm), _p(t_sn), M, N,
+                                          1 / 4096, 1 / 8192, layout, _p(y_r)) == 0
+    y_o = oracle.dequantize(flat, sm, sn, None, layout=layout, shape=(M, N))[1]
+    assert oracle.ulp_diff_f16(y_r.cpu().numpy(), y_o).max() == 0
+
+
+@pytest.mark.parametrize("M,N,K,requant", [(16, 4096, 4096, False), (128, 12288, 4096, True), (200, 1024, 2048, False)])
+def test_linear_three_way(cuda, oracle, ref, M, N, K, requant):
+    """quantize -> column_parallel_linear(gather_output=true) [-> quantize] through the reference's own
+    operators (cuBLASLt int8 GEMM inside) vs the oracle vs this library's fused path."""
+    import pplb200
+    rng = np.random.default_rng(M + N + K)
+    x = _x(rng, M, K, "normal")
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    sn = (rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float16)
+    tx, tw, tsn, tb = _t(cuda, x), _t(cuda, w), _t(cuda, sn), _t(cuda, bias)
+    xq = cuda.empty((M, K), dtype=cuda.int8, device="cuda")
+    sm = cuda.empty((M,), dtype=cuda.float16, device="cuda")
+    acc = cuda.empty((M, N), dtype=cuda.int32, device="cuda")
+    y_r = cuda.empty((M, N), dtype=cuda.float16, device="cuda")
+    ws = cuda.empty((32 << 20,), dtype=cuda.uint8, device="cuda")
+    assert ref.ref_minmax_quantize_fp16(None, _p(tx), M, K, 4096.0, 0, _p(xq), _p(sm)) == 0
+    assert ref.ref_column_parallel_linear(None, _p(xq), _p(tw), _p(tb), _p(sm), _p(tsn), 1 / 4096, 1 / 8192, M, N, K, 1,
+                                          _p(acc), _p(ws), ws.numel(), _p(y_r)) == 0
+    o = oracle.linear(x, w, sn, bias, requant=requant)
+    cuda.cuda.synchronize()
+    assert np.array_equal(acc.cpu().numpy(), o["acc"]), "cuBLASLt int32 accumulators vs oracle"
+    assert oracle.ulp_diff_f16(y_r.cpu().numpy(), o["y"]).max() == 0, "reference fp16 output vs oracle"
+
+    lin = pplb200.W8A8Linear(tw, tsn, tb, max_tokens=M, requant=requant)
+    out = lin(tx)
+    y_m = out[0] if requant else out
+    cuda.cuda.synchronize()
+    assert cuda.equal(y_r.view(cuda.int16), y_m.view(cuda.int16)), "reference fp16 output vs library"
+    if requant:
+        yq_r = cuda.empty((M, N), dtype=cuda.int8, device="cuda")
+        ys_r = cuda.empty((M,), dtype=cuda.float16, device="cuda")
+        assert ref.ref_minmax_quantize_fp16(None, _p(y_r), M, N, 4096.0, 0, _p(yq_r), _p(ys_r)) == 0
+        assert cuda.equal(yq_r, out[1]) and cuda.equal(ys_r.view(cuda.int16), out[2].view(cuda.int16))
+        assert np.array_equal(yq_r.cpu().numpy(), o["yq"])
+
+
+def test_reference_raw_int32_mode(cuda, oracle, ref):
+    """gather_output = false: both return the raw int32 accumulators in `output`."""
+    import pplb200
+    rng = np.random.default_rng(5)
+    M, N, K = 64, 256, 512
+    a = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    ta, tw = _t(cuda, a), _t(cuda, w)
+    out_r = cuda.empty((M, N), dtype=cuda.int32, device="cuda")
+    ws = cuda.empty((32 << 20,), dtype=cuda.uint8, device="cuda")
+    assert ref.ref_column_parallel_linear(None, _p(ta), _p(tw), None, None, None, 1.0, 1.0, M, N, K, 0, None, _p(ws),
+                                          ws.numel(), _p(out_r)) == 0
+    out_m = pplb200.column_parallel_linear(ta, tw, None, None, None, K, N, gather_output=False)
+    assert cuda.equal(out_r, out_m)
+    assert np.array_equal(out_r.cpu().numpy(), oracle.gemm(a, w))
