@@ -62,10 +62,12 @@ int32_t check_gemm_args(const void* A, int64_t lda, const void* B, int64_t ldb, 
 
 } // namespace
 
+// chained: the caller has just enqueued the activation quantizer on `stream`, which also cleared the
+// row-maximum scratch; the GEMM and the re-quantizer are then launched as programmatic dependents.
 int32_t gemm_entry(cudaStream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N,
                    int64_t K, int32_t mode, const void* scale_M, const void* scale_N, const void* bias, float down_M,
                    float down_N, float requant_up, void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q,
-                   void* out_q_scale) {
+                   void* out_q_scale, bool chained) {
     int32_t rc = check_gemm_args(A, lda, B, ldb, M, N, K, mode, scale_M, scale_N, bias, out, ldc, out_q, out_q_scale);
     if (rc != RC_SUCCESS || M == 0 || N == 0) return rc;
     GemmArgs g;
@@ -79,13 +81,15 @@ int32_t gemm_entry(cudaStream_t stream, const void* A, int64_t lda, const void* 
         const int64_t need = gemm_ws_bytes(M, mode);
         if (!ws || ws_bytes < need) return fail(RC_INVALID_VALUE, "workspace too small: %lld < %lld", (long long)ws_bytes, (long long)need);
         g.row_absmax_bits = (uint32_t*)ws;
-        if (cudaMemsetAsync(ws, 0, (size_t)M * 4, stream) != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
+        if (!chained && cudaMemsetAsync(ws, 0, (size_t)M * 4, stream) != cudaSuccess)
+            return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
     }
+    g.pdl = chained;
     rc = launch_gemm(stream, g);
     if (rc != RC_SUCCESS) return rc;
     if (mode == EPI_DEQUANT_F16_REQUANT_I8)
         rc = launch_quantize(stream, (const half*)out, M, N, requant_up, LAYOUT_ROW_MAJOR, (int8_t*)out_q,
-                             (half*)out_q_scale, g.row_absmax_bits);
+                             (half*)out_q_scale, g.row_absmax_bits, nullptr, /*pdl=*/M <= 128);
     return rc;
 }
 
@@ -139,7 +143,7 @@ int32_t pplb200_i8i8_gemm(pplb200_stream_t stream, const void* A, int64_t lda, c
                           float down_scale_M, float down_scale_N, float requant_up_scale,
                           void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q, void* out_q_scale) {
     return gemm_entry((cudaStream_t)stream, A, lda, B, ldb, M, N, K, epilogue_mode, scale_M, scale_N, optional_bias,
-                      down_scale_M, down_scale_N, requant_up_scale, ws, ws_bytes, out, ldc, out_q, out_q_scale);
+                      down_scale_M, down_scale_N, requant_up_scale, ws, ws_bytes, out, ldc, out_q, out_q_scale, false);
 }
 
 int64_t pplb200_i8i8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode) {
@@ -163,10 +167,16 @@ int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const v
     void* xq = base;
     void* sm = base + round_up(M * K, WS_ALIGN);
     void* gws = base + round_up(M * K, WS_ALIGN) + round_up(M * 2, WS_ALIGN);
-    int32_t rc = pplb200_i8i8_minmax_quantize_fp16(stream, x, M, K, up_scale, LAYOUT_ROW_MAJOR, xq, sm);
+    if (K % 16) return fail(RC_INVALID_VALUE, "K must be a multiple of 16, got %lld", (long long)K);
+    if (!x || !aligned16(x)) return fail(RC_INVALID_VALUE, "x must be a 16-byte aligned device pointer");
+    if (M > 0x7fffffffLL) return fail(RC_UNSUPPORTED, "M beyond 2^31 - 1");
+    // the quantizer also clears the row-maximum scratch of the fused re-quantize
+    uint32_t* absmax = epilogue_mode == EPI_DEQUANT_F16_REQUANT_I8 ? (uint32_t*)gws : nullptr;
+    int32_t rc = launch_quantize((cudaStream_t)stream, (const half*)x, M, K, up_scale, LAYOUT_ROW_MAJOR, (int8_t*)xq,
+                                 (half*)sm, nullptr, absmax, false);
     if (rc != RC_SUCCESS) return rc;
     return gemm_entry((cudaStream_t)stream, xq, K, W, K, M, N, K, epilogue_mode, sm, scale_N, optional_bias, down_scale_M,
-                      down_scale_N, requant_up_scale, gws, gemm_ws_bytes(M, epilogue_mode), y, N, y_q, y_q_scale);
+                      down_scale_N, requant_up_scale, gws, gemm_ws_bytes(M, epilogue_mode), y, N, y_q, y_q_scale, true);
 }
 
 int32_t pplb200_i8i8_gemm_status(int32_t reset) { return gemm_status(reset); }

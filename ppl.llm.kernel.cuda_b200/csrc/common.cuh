@@ -65,8 +65,12 @@ __host__ __device__ inline int64_t layout_offset(int32_t layout, int64_t rows, i
 
 // ---- kernels / launchers implemented across the translation units ----
 
+// given_absmax_bits != null: rows are quantized with that precomputed max |x| (float bits) instead of
+// scanning the row.  zero_absmax_bits != null: the kernel also clears that per-row array (for the
+// GEMM that follows).  pdl: launch as a programmatic dependent of the preceding kernel in the stream.
 int32_t launch_quantize(cudaStream_t stream, const half* in, int64_t batch, int64_t dim, float up_scale,
-                        int32_t layout, int8_t* q, half* scale, const uint32_t* given_absmax_bits);
+                        int32_t layout, int8_t* q, half* scale, const uint32_t* given_absmax_bits,
+                        uint32_t* zero_absmax_bits = nullptr, bool pdl = false);
 
 int32_t launch_dequantize(cudaStream_t stream, const int32_t* acc, const half* bias, const half* scale_m,
                           const half* scale_n, int64_t batch, int64_t dim, float down_m, float down_n,
@@ -83,7 +87,9 @@ struct GemmArgs {
     float down_m, down_n;
     void* out; int64_t ldc;
     uint32_t* row_absmax_bits; // mode 2: per-row max |y| as float bits, zeroed by the launcher
+    bool pdl = false;          // launch as a programmatic dependent of the preceding kernel
 };
+int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int* status, bool pdl);
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);
 int32_t gemm_status(int32_t reset);
 

@@ -330,6 +330,9 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     if (a.M > INT32_MAX - BM || a.N > INT32_MAX - 256 || a.K > INT32_MAX - BK)
         return fail(RC_UNSUPPORTED, "GEMM extent beyond 2^31");
 
+    // Up to 128 tokens the op is bound by the weight stream: dedicated small-batch kernel.
+    if (a.M <= 128) return launch_gemm_decode(stream, a, dev->status, a.pdl);
+
     // Tile width: the widest tile that still gives every SM work.
     const int64_t m_tiles = (a.M + BM - 1) / BM;
     int bn = 32;

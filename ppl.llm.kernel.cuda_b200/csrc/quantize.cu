@@ -21,6 +21,9 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
     return v;
 }
 
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float block_max(float v, float* red, int nwarps) {
 #pragma unroll
     for (int m = 16; m >= 1; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
@@ -51,16 +54,22 @@ __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
 template <int UNITS>
 __global__ void __launch_bounds__(QTPB)
 quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, float up_scale, int32_t layout,
-                     int8_t* __restrict__ q, half* __restrict__ scale_out, const uint32_t* __restrict__ given_absmax_bits) {
+                     int8_t* __restrict__ q, half* __restrict__ scale_out, const uint32_t* __restrict__ given_absmax_bits,
+                     uint32_t* __restrict__ zero_absmax_bits) {
     __shared__ float red[QTPB / 32];
     const int64_t row = blockIdx.x;
     const int units = (int)(dim >> 4);
     const uint4* src = reinterpret_cast<const uint4*>(in + row * dim);
+    // With a precomputed row maximum the row may be split over blockIdx.y; otherwise gridDim.y == 1.
+    const int unit_base = blockIdx.y * blockDim.x * UNITS;
+
+    pdl_launch_dependents(); // a dependent kernel may start its own preamble now
+    pdl_wait_prior_grid();   // no-op unless launched as a programmatic dependent
 
     uint4 v[UNITS][2];
 #pragma unroll
     for (int u = 0; u < UNITS; ++u) {
-        const int unit = u * blockDim.x + threadIdx.x;
+        const int unit = unit_base + u * blockDim.x + threadIdx.x;
         if (unit < units) {
             v[u][0] = ldg_stream(src + 2 * unit);
             v[u][1] = ldg_stream(src + 2 * unit + 1);
@@ -92,7 +101,7 @@ quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, fl
 
 #pragma unroll
     for (int u = 0; u < UNITS; ++u) {
-        const int unit = u * blockDim.x + threadIdx.x;
+        const int unit = unit_base + u * blockDim.x + threadIdx.x;
         if (unit < units) {
             const __half2* h = reinterpret_cast<const __half2*>(&v[u][0]);
             int qi[16];
@@ -111,7 +120,10 @@ quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, fl
             *reinterpret_cast<uint4*>(q + off) = o;
         }
     }
-    if (threadIdx.x == 0) scale_out[row] = __float2half_rn(scale * up_scale);
+    if (threadIdx.x == 0 && blockIdx.y == 0) {
+        scale_out[row] = __float2half_rn(scale * up_scale);
+        if (zero_absmax_bits != nullptr) zero_absmax_bits[row] = 0u;
+    }
 }
 
 // Rows too long for the register-resident kernel: classic two-pass (second read hits L2 for
@@ -119,8 +131,10 @@ quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, fl
 __global__ void __launch_bounds__(QTPB)
 quantize_rows_twopass_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, float up_scale, int32_t layout,
                              int8_t* __restrict__ q, half* __restrict__ scale_out,
-                             const uint32_t* __restrict__ given_absmax_bits) {
+                             const uint32_t* __restrict__ given_absmax_bits, uint32_t* __restrict__ zero_absmax_bits) {
     __shared__ float red[QTPB / 32];
+    pdl_launch_dependents();
+    pdl_wait_prior_grid();
     const int64_t row = blockIdx.x;
     const int64_t units = dim >> 4;
     const uint4* src = reinterpret_cast<const uint4*>(in + row * dim);
@@ -156,7 +170,10 @@ quantize_rows_twopass_kernel(const half* __restrict__ in, int64_t batch, int64_t
         o.w = pack4(qi[12], qi[13], qi[14], qi[15]);
         *reinterpret_cast<uint4*>(q + layout_offset(layout, batch, dim, row, unit << 4)) = o;
     }
-    if (threadIdx.x == 0) scale_out[row] = __float2half_rn(scale * up_scale);
+    if (threadIdx.x == 0) {
+        scale_out[row] = __float2half_rn(scale * up_scale);
+        if (zero_absmax_bits != nullptr) zero_absmax_bits[row] = 0u;
+    }
 }
 
 // ---- dequantize ------------------------------------------------------------------------------
@@ -242,30 +259,55 @@ int grid_for(int64_t work_items, int tpb) {
     return (int)blocks;
 }
 
+template <typename... Args>
+cudaError_t launch_ex(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 } // namespace
 
 int32_t launch_quantize(cudaStream_t stream, const half* in, int64_t batch, int64_t dim, float up_scale,
-                        int32_t layout, int8_t* q, half* scale, const uint32_t* given_absmax_bits) {
+                        int32_t layout, int8_t* q, half* scale, const uint32_t* given_absmax_bits,
+                        uint32_t* zero_absmax_bits, bool pdl) {
     if (batch == 0 || dim == 0) return RC_SUCCESS;
     const int64_t units = dim >> 4;
-    const unsigned grid = (unsigned)batch;
-    if (units <= QTPB * 8) {
+    cudaError_t e;
+    if (given_absmax_bits != nullptr && units <= (int64_t)QTPB * 65535) {
+        // the row maximum is known: no reduction, so a row is spread over as many CTAs as it has
+        // 256-unit chunks (more loads in flight when there are few rows)
+        int threads = (int)(units < QTPB ? (units + 31) / 32 * 32 : QTPB);
+        const dim3 grid((unsigned)batch, (unsigned)((units + threads - 1) / threads), 1);
+        e = launch_ex(quantize_rows_kernel<1>, grid, dim3(threads), stream, pdl, in, batch, dim, up_scale, layout, q, scale,
+                      given_absmax_bits, zero_absmax_bits);
+    } else if (units <= QTPB * 8) {
         // threads: enough to give every thread the same small number of units
         int per = (int)((units + QTPB - 1) / QTPB);
         int bucket = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
         int threads = (int)((units + bucket - 1) / bucket);
         threads = (threads + 31) / 32 * 32;
         if (threads > QTPB) threads = QTPB;
+        const dim3 grid((unsigned)batch, 1, 1), block(threads);
         switch (bucket) {
-        case 1: quantize_rows_kernel<1><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
-        case 2: quantize_rows_kernel<2><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
-        case 4: quantize_rows_kernel<4><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
-        default: quantize_rows_kernel<8><<<grid, threads, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits); break;
+        case 1: e = launch_ex(quantize_rows_kernel<1>, grid, block, stream, pdl, in, batch, dim, up_scale, layout, q, scale, given_absmax_bits, zero_absmax_bits); break;
+        case 2: e = launch_ex(quantize_rows_kernel<2>, grid, block, stream, pdl, in, batch, dim, up_scale, layout, q, scale, given_absmax_bits, zero_absmax_bits); break;
+        case 4: e = launch_ex(quantize_rows_kernel<4>, grid, block, stream, pdl, in, batch, dim, up_scale, layout, q, scale, given_absmax_bits, zero_absmax_bits); break;
+        default: e = launch_ex(quantize_rows_kernel<8>, grid, block, stream, pdl, in, batch, dim, up_scale, layout, q, scale, given_absmax_bits, zero_absmax_bits); break;
         }
     } else {
-        quantize_rows_twopass_kernel<<<grid, QTPB, 0, stream>>>(in, batch, dim, up_scale, layout, q, scale, given_absmax_bits);
+        e = launch_ex(quantize_rows_twopass_kernel, dim3((unsigned)batch), dim3(QTPB), stream, pdl, in, batch, dim, up_scale, layout, q, scale,
+                      given_absmax_bits, zero_absmax_bits);
     }
-    return check_launch("quantize");
+    if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "quantize launch failed: %s", cudaGetErrorString(e));
+    return RC_SUCCESS;
 }
 
 int32_t launch_dequantize(cudaStream_t stream, const int32_t* acc, const half* bias, const half* scale_m,

@@ -56,7 +56,7 @@ namespace pplb200 {
 int32_t gemm_entry(cudaStream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N,
                    int64_t K, int32_t mode, const void* scale_M, const void* scale_N, const void* bias, float down_M,
                    float down_N, float requant_up, void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q,
-                   void* out_q_scale);
+                   void* out_q_scale, bool chained = false);
 }
 
 using namespace pplb200;
