@@ -128,34 +128,60 @@ def _max_over_ranks(ms, world):
     return float(t.item())
 
 
-def _time_steps(fn, steps, warmup, world):
-    """fn(i) enqueues step i on the current stream.  Returns ms for `steps` steps (max over ranks)."""
+def _time_steps(runner, steps, warmup, world):
+    """runner.run(first, count) enqueues `count` steps on the current stream.  Returns ms for exactly
+    `steps` steps after `warmup` untimed ones (CUDA events, max over ranks)."""
     import torch
-    for i in range(warmup):
-        fn(i)
+    runner.run(0, warmup)
     _barrier(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        fn(warmup + i)
+    # start the timed region on a round boundary so that whole-round graphs can be used
+    first = -(-warmup // getattr(runner, "nsets", 1)) * getattr(runner, "nsets", 1)
+    runner.run(first, steps)
     e1.record()
     _barrier(world)
     return _max_over_ranks(e0.elapsed_time(e1), world)
 
 
-def _capture(fn, nsets):
-    """Captures fn(s) for every buffer set s into its own CUDA graph; returns replay(i)."""
-    import torch
-    graphs = []
-    for s in range(nsets):
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
-            fn(s)
-        graphs.append(g)
+class _Captured:
+    """CUDA-graph form of fn(s): one graph per buffer set plus one "round" graph that runs all the
+    sets back to back.  run(first, count) enqueues exactly `count` consecutive steps starting at
+    step index `first`, using round graphs where a whole round fits, so the host's launch cost
+    is paid once per round instead of once per microsecond-scale step."""
 
-    def replay(i, _keep=fn):  # _keep: the captured closure owns the buffers the graphs point into
-        graphs[i % nsets].replay()
-    return replay
+    def __init__(self, fn, nsets):
+        import torch
+        self.fn, self.nsets = fn, nsets  # fn owns the buffers the graphs point into
+        self.single = []
+        for s in range(nsets):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn(s)
+            self.single.append(g)
+        self.round = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.round):
+            for s in range(nsets):
+                fn(s)
+
+    def run(self, first, count):
+        i, end = first, first + count
+        while i < end:
+            if i % self.nsets == 0 and end - i >= self.nsets:
+                self.round.replay()
+                i += self.nsets
+            else:
+                self.single[i % self.nsets].replay()
+                i += 1
+
+
+class _Eager:
+    def __init__(self, fn):
+        self.fn = fn
+
+    def run(self, first, count):
+        for i in range(first, first + count):
+            self.fn(i)
 
 
 class Workload:
@@ -403,10 +429,10 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
         if kernel_only:
             kernel_only(s)
     torch.cuda.synchronize()
-    if use_graphs:
-        step, e2e = _capture(step, wk.nsets), _capture(e2e, wk.nsets)
-        if kernel_only:
-            kernel_only = _capture(kernel_only, wk.nsets)
+    wrap = (lambda f: _Captured(f, wk.nsets)) if use_graphs else _Eager
+    step, e2e = wrap(step), wrap(e2e)
+    if kernel_only:
+        kernel_only = wrap(kernel_only)
     ms = _time_steps(step, args.steps, args.warmup, world)
     ms_e2e = _time_steps(e2e, args.steps, args.warmup, world)
     ms_k = _time_steps(kernel_only, args.steps, args.warmup, 1) if kernel_only else None
@@ -436,7 +462,7 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
             "sharding": ("replicas only (x%d)" % world) if wk.shard is None and world > 1 else
                         ("none" if wk.shard is None else "%s-parallel over %d GPUs" % (wk.shard, world)),
             "l2": wk.l2_note,
-            "launch": "one CUDA graph replay per step" if use_graphs else "eager launches",
+            "launch": ("CUDA graph replay, %d steps (one per buffer set) per graph" % wk.nsets) if use_graphs else "eager launches",
             "algorithmic_bytes_per_step": wl.algorithmic_bytes(name),
             "gb_per_s": wl.algorithmic_bytes(name) * replicas / (per_step * 1e-3) / 1e9 if wk.shard is None else None,
         },

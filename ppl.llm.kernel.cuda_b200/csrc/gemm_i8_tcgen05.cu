@@ -17,6 +17,7 @@
 #include "ptx.cuh"
 
 #include <mutex>
+#include <stdlib.h>
 
 namespace pplb200 {
 
@@ -25,8 +26,11 @@ namespace {
 constexpr int BM = 128;       // tile rows (TMEM lanes)
 constexpr int BK = 128;       // bytes (= int8 elements) of K per stage: one 128-byte swizzle row
 constexpr int UMMA_K = 32;    // K per tcgen05.mma kind::i8
-constexpr int NUM_THREADS = 192;
-constexpr int EPI_WARP0 = 2;
+// warp 0: TMA producer, warp 1: MMA issuer, warps 2..: epilogue.  Four epilogue warps (one per TMEM
+// lane quarter) drain a 128 x 256 accumulator faster than its successor is produced; on the
+// power-capped part eight warps measured slower (more issue activity, lower clocks).
+constexpr int EPI_WARPS = 4;
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 
 // status bits recorded when a bounded wait gives up
 constexpr unsigned ST_PRODUCER_TIMEOUT = 1u, ST_MMA_FULL_TIMEOUT = 2u, ST_MMA_ACC_TIMEOUT = 4u, ST_EPI_TIMEOUT = 8u;
@@ -106,7 +110,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_addr(&acc_full_bar[b]), 1);
-            ptx::mbar_init(ptx::smem_addr(&acc_empty_bar[b]), 4);
+            ptx::mbar_init(ptx::smem_addr(&acc_empty_bar[b]), EPI_WARPS);
         }
         ptx::fence_mbar_init();
     }
@@ -179,6 +183,11 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     } else {
         // ------------------------------------------------------------------ epilogue
         const int quarter = warp & 3; // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
+        // with more than four epilogue warps, warps sharing a lane quarter split the tile's columns
+        constexpr int COL_GROUPS = EPI_WARPS / 4;
+        constexpr int GROUP_COLS = (BN / COL_GROUPS) >= 32 ? BN / COL_GROUPS : BN;
+        const int col_begin = ((warp - 2) >> 2) * GROUP_COLS;
+        const int col_end = col_begin + GROUP_COLS < BN ? col_begin + GROUP_COLS : BN;
         const bool has_bias = p.bias != nullptr;
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
@@ -196,7 +205,7 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
 
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
                 const int n0 = n_tile * BN + c0;
                 if (n0 >= p.N) break; // warp-uniform
                 uint32_t acc[32];
@@ -233,6 +242,193 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+
+// ---- CTA-pair variant ---------------------------------------------------------------------------
+// Two CTAs of a cluster compute one 256 x 256 tile with tcgen05.mma.cta_group::2: each CTA stages
+// its own 128 rows of A and its own 128 rows of B (half of the tile's N), the leader issues the
+// MMAs, and each CTA's tensor memory receives its 128 rows of the accumulator.  Per CTA a K block
+// then costs 32 KiB of operand traffic for the same 128 tensor-core cycles x 4 that the single-CTA
+// 128 x 256 tile pays 48 KiB for -- the single-CTA tile is limited by the L2 -> SM operand
+// bandwidth, this one is not.  No TMA multicast: every CTA fetches its own halves.
+struct PairCfg {
+    static constexpr int BN = 256;
+    static constexpr int HALF_N = 128;
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int B_BYTES = HALF_N * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // per CTA
+    static constexpr int STAGES = 6;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+    static constexpr int TMEM_COLS = 512;                   // two accumulator buffers of 256 columns
+};
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                            const KernelParams p) {
+    using C = PairCfg;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[C::STAGES];   // used in the leader: both CTAs' tiles have landed
+    __shared__ __align__(8) uint64_t empty_bar[C::STAGES];  // per CTA: the MMAs reading this slot retired
+    __shared__ __align__(8) uint64_t acc_full_bar[2];       // per CTA: accumulator buffer complete
+    __shared__ __align__(8) uint64_t acc_empty_bar[2];      // used in the leader: both CTAs drained the buffer
+    __shared__ uint32_t tmem_base_slot;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t ring = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t rank = ptx::cluster_ctarank();
+    const bool leader = rank == 0;
+
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmap_a);
+        ptx::prefetch_tensormap(&tmap_b);
+        for (int s = 0; s < C::STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_addr(&full_bar[s]), 1);
+            ptx::mbar_init(ptx::smem_addr(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            ptx::mbar_init(ptx::smem_addr(&acc_full_bar[b]), 1);
+            ptx::mbar_init(ptx::smem_addr(&acc_empty_bar[b]), 2 * EPI_WARPS); // the epilogue warps of both CTAs
+        }
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_addr(&tmem_base_slot), C::TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    ptx::cluster_sync_all(); // barriers of both CTAs are initialised before anyone signals them
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    const int num_pairs = (int)(gridDim.x >> 1);
+    const int pair_id = (int)(blockIdx.x >> 1);
+    const int num_tiles = p.num_m_tiles * p.num_n_tiles; // tiles of 256 x 256
+    const int nkb = p.num_k_blocks;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+                const int m_tile = tile % p.num_m_tiles;
+                const int n_tile = tile / p.num_m_tiles;
+                const int row_a = m_tile * 256 + (int)rank * BM;
+                const int row_b = n_tile * C::BN + (int)rank * C::HALF_N;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_addr(&empty_bar[stage]), phase ^ 1u, p.status, ST_PRODUCER_TIMEOUT)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full_local = ptx::smem_addr(&full_bar[stage]);
+                    const uint32_t full_leader = ptx::map_to_cta(full_local, 0);
+                    const uint32_t sa = ring + stage * C::STAGE_BYTES;
+                    if (leader) ptx::mbar_arrive_expect_tx(full_local, 2 * C::STAGE_BYTES);
+                    ptx::tma_load_2d_pair(sa, &tmap_a, full_leader, kb * BK, row_a);
+                    ptx::tma_load_2d_pair(sa + C::A_BYTES, &tmap_b, full_leader, kb * BK, row_b);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = ptx::make_i8_idesc(256, C::BN);
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int it = 0;
+            for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
+                const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+                if (!ptx::mbar_wait(ptx::smem_addr(&acc_empty_bar[buf]), acc_phase ^ 1u, p.status, ST_MMA_ACC_TIMEOUT)) break;
+                ptx::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + buf * C::BN;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_addr(&full_bar[stage]), phase, p.status, ST_MMA_FULL_TIMEOUT)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ring + stage * C::STAGE_BYTES;
+                    const uint64_t adesc = ptx::make_kmajor_sw128_desc(sa);
+                    const uint64_t bdesc = ptx::make_kmajor_sw128_desc(sa + C::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        ptx::mma_i8_pair(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    // free the slot in both CTAs once these MMAs retire
+                    const uint32_t empty_local = ptx::smem_addr(&empty_bar[stage]);
+                    ptx::mma_commit_pair(empty_local);
+                    ptx::mma_commit_pair(ptx::map_to_cta(empty_local, 1));
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) {
+                    const uint32_t accf = ptx::smem_addr(&acc_full_bar[buf]);
+                    ptx::mma_commit_pair(accf);
+                    ptx::mma_commit_pair(ptx::map_to_cta(accf, 1));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        const int quarter = warp & 3;
+        const int col_begin = ((warp - 2) >> 2) * (C::BN / (EPI_WARPS / 4)), col_end = col_begin + C::BN / (EPI_WARPS / 4);
+        const bool has_bias = p.bias != nullptr;
+        int it = 0;
+        for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
+            const int m_tile = tile % p.num_m_tiles;
+            const int n_tile = tile / p.num_m_tiles;
+            const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+            if (!ptx::mbar_wait(ptx::smem_addr(&acc_full_bar[buf]), acc_phase, p.status, ST_EPI_TIMEOUT)) break;
+            ptx::tc_fence_after();
+
+            const int row = m_tile * 256 + (int)rank * BM + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            float batch_scale = 0.0f;
+            if (p.mode != EPI_RAW_I32 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
+            __half absmax = __float2half_rn(0.0f);
+            const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::BN;
+
+#pragma unroll 1
+            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+                const int n0 = n_tile * C::BN + c0;
+                if (n0 >= p.N) break; // warp-uniform
+                uint32_t acc[32];
+                ptx::tmem_ld_32x32(taddr_row + c0, acc);
+                ptx::tmem_ld_wait();
+                if (!row_ok) continue;
+                if (p.mode == EPI_RAW_I32) {
+                    int32_t* dst = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldc + n0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        if (n0 + j < p.N)
+                            *reinterpret_cast<uint4*>(dst + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                } else {
+                    half* dst = reinterpret_cast<half*>(p.out) + (int64_t)row * p.ldc + n0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8)
+                        if (n0 + j < p.N)
+                            *reinterpret_cast<uint4*>(dst + j) =
+                                dequant8(acc + j, p.scale_n + n0 + j, p.bias + n0 + j, p.down_n, batch_scale, has_bias, absmax);
+                }
+            }
+            if (p.mode == EPI_DEQUANT_F16_REQUANT_I8 && row_ok)
+                atomicMax(p.row_absmax_bits + row, __float_as_uint(__half2float(absmax)));
+
+            // this CTA's half of the accumulator buffer is drained: tell the leader's MMA thread
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
+        }
+    }
+
+    // Neither CTA may leave while its partner can still read its shared memory or signal its barriers.
+    ptx::tc_fence_before();
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
     }
 }
 
@@ -294,6 +490,8 @@ const DeviceInfo* device_info() {
         if (cudaGetSymbolAddress(&addr, g_gemm_status) != cudaSuccess) return nullptr;
         d.status = static_cast<unsigned int*>(addr);
         if (!set_smem_attr<256>() || !set_smem_attr<128>() || !set_smem_attr<64>() || !set_smem_attr<32>()) return nullptr;
+        if (cudaFuncSetAttribute(gemm_i8_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PairCfg::SMEM_BYTES) != cudaSuccess) return nullptr;
         d.ready = true;
     }
     return &d;
@@ -321,6 +519,42 @@ int32_t launch_bn(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev)
     return check_launch("gemm_i8_tcgen05");
 }
 
+// 256 x 256 tiles on CTA pairs (clusters of two), persistent: one pair per two SMs.
+int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev) {
+    CUtensorMap ta, tb;
+    if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
+    if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, PairCfg::HALF_N)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
+    KernelParams p;
+    p.M = (int32_t)a.M; p.N = (int32_t)a.N;
+    p.num_m_tiles = (int32_t)((a.M + 255) / 256);
+    p.num_n_tiles = (int32_t)((a.N + PairCfg::BN - 1) / PairCfg::BN);
+    p.num_k_blocks = (int32_t)((a.K + BK - 1) / BK);
+    p.mode = a.mode;
+    p.out = a.out; p.ldc = a.ldc;
+    p.scale_m = a.scale_m; p.scale_n = a.scale_n; p.bias = a.bias;
+    p.down_m = a.down_m; p.down_n = a.down_n;
+    p.row_absmax_bits = a.row_absmax_bits;
+    p.status = dev.status;
+    const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
+    int64_t pairs = dev.sms / 2;
+    if (tiles < pairs) pairs = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel, ta, tb, p);
+    if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "pair GEMM launch failed: %s", cudaGetErrorString(e));
+    return RC_SUCCESS;
+}
+
 } // namespace
 
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
@@ -332,6 +566,10 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
 
     // Up to 128 tokens the op is bound by the weight stream: dedicated small-batch kernel.
     if (a.M <= 128) return launch_gemm_decode(stream, a, dev->status, a.pdl);
+
+    // Large problems: 256 x 256 tiles on CTA pairs, as long as every pair gets at least one tile.
+    if (((a.M + 255) / 256) * ((a.N + 255) / 256) >= dev->sms / 2 && getenv("PPLB200_DEBUG_NOPAIR") == nullptr)
+        return launch_pair(stream, a, *dev);
 
     // Tile width: the widest tile that still gives every SM work.
     const int64_t m_tiles = (a.M + BM - 1) / BM;

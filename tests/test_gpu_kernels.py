@@ -121,7 +121,8 @@ def test_dequantize_error_codes(cuda):
 
 
 GEMM_SHAPES = [(1, 8, 16), (16, 32, 128), (128, 256, 128), (128, 256, 512), (130, 264, 144), (257, 520, 1040),
-               (16, 4096, 4096), (128, 12288, 4096), (300, 1000, 2048), (512, 4096, 1024), (1024, 2048, 3584)]
+               (16, 4096, 4096), (128, 12288, 4096), (300, 1000, 2048), (512, 4096, 1024), (1024, 2048, 3584),
+               (2300, 2120, 272), (2048, 2560, 144), (4096, 2752, 512)]  # the last three: 256 x 256 tiles on CTA pairs
 
 
 def _exact_gemm(torch, a, b):
@@ -168,7 +169,8 @@ def test_gemm_strided_operands(cuda):
     assert cuda.equal(c, _exact_gemm(cuda, a, b))
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (130, 264, 144), (128, 12288, 4096), (257, 528, 1040)])
+@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (130, 264, 144), (128, 12288, 4096), (257, 528, 1040),
+                                   (2300, 2120, 272)])
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_gemm_dequant_epilogue(cuda, oracle, M, N, K, with_bias):
     import pplb200
@@ -186,7 +188,7 @@ def test_gemm_dequant_epilogue(cuda, oracle, M, N, K, with_bias):
     assert d.max() == 0, "max ulp %d" % d.max()
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (128, 12288, 4096), (70, 272, 256)])
+@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (128, 12288, 4096), (70, 272, 256), (2300, 2128, 272)])
 def test_gemm_requant_epilogue(cuda, oracle, M, N, K):
     import pplb200
     rng = np.random.default_rng(M + N + K)
