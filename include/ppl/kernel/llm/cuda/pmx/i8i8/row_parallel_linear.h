@@ -60,7 +60,7 @@ inline ppl::common::RetCode row_parallel_linear(
     }
     const int64_t M = (int64_t)input_shape->CalcElementsToDimensionExcludingPadding(input_shape->GetDimCount() - 1);
     return (ppl::common::RetCode)pplb200_i8i8_row_parallel_linear(
-        (pplb200_stream_t)stream, input, M, weight, bias, scale_M, scale_N, down_scale_M, down_scale_N,
+        (pplb200_stream_t)stream, input, M, /*input_ld=*/0, weight, bias, scale_M, scale_N, down_scale_M, down_scale_N,
         in_features, out_features, (int32_t)weight_layout, nccl_param->rank, nccl_param->size,
         (void*)nccl_param->comm, input_is_parallel ? 1 : 0, (int32_t)reduce, quant_buffer,
         cublas_workspace, cublas_workspace_size, output);

@@ -127,14 +127,16 @@ int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream, const void*
 /*
  * Row parallel: replaces ppl::kernel::llm::cuda::pmx::i8i8::row_parallel_linear
  *   (include/.../pmx/i8i8/row_parallel_linear.h:33-58; src/.../pmx/i8i8/row_parallel_linear.cu:28-162).
- * input int8 [M, K/size]; weight int8 [N, K/size]; quant_buffer int32 [M, N] (required when size > 1).
+ * input int8 [M, K/size] with `input_ld` bytes between rows (K/size when the shard is contiguous, as in
+ *   the reference; K when it is a column slice of the full quantized activation [M, K]; 0 means
+ *   contiguous); weight int8 [N, K/size]; quant_buffer int32 [M, N] (required when size > 1).
  * reduce_mode 0 (exact, default): int32 partial accumulators are summed across ranks BEFORE the
  *   dequant epilogue, so the result is bit-identical to the unsharded linear; every rank passes
  *   the full-row scale_M and the same bias.
  * reduce_mode 1 (reference order): dequantize each partial to fp16, bias on rank 0 only, then fp16
  *   all-reduce (src/.../pmx/i8i8/row_parallel_linear.cu:84,131-158).
  */
-int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream, const void* input, int64_t M,
+int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream, const void* input, int64_t M, int64_t input_ld,
                                          const void* weight, const void* optional_bias,
                                          const void* scale_M, const void* scale_N,
                                          float down_scale_M, float down_scale_N,

@@ -19,7 +19,6 @@
 #include "ptx.cuh"
 
 #include <mutex>
-#include <stdlib.h>
 
 namespace pplb200 {
 
@@ -473,7 +472,6 @@ int32_t launch_bt(cudaStream_t stream, const GemmArgs& a, const DecDeviceInfo& d
     if (S > 8) S = 8;
     if (S > p.num_k_blocks / 2) S = p.num_k_blocks / 2;
     if (S < 1) S = 1;
-    if (const char* e = getenv("PPLB200_DEBUG_SPLIT")) { S = atoi(e); } // TEMP tuning probe
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)S, (unsigned)n_tiles, 1);

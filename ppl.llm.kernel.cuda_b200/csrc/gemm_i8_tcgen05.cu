@@ -17,7 +17,6 @@
 #include "ptx.cuh"
 
 #include <mutex>
-#include <stdlib.h>
 
 namespace pplb200 {
 
@@ -568,7 +567,7 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     if (a.M <= 128) return launch_gemm_decode(stream, a, dev->status, a.pdl);
 
     // Large problems: 256 x 256 tiles on CTA pairs, as long as every pair gets at least one tile.
-    if (((a.M + 255) / 256) * ((a.N + 255) / 256) >= dev->sms / 2 && getenv("PPLB200_DEBUG_NOPAIR") == nullptr)
+    if (((a.M + 255) / 256) * ((a.N + 255) / 256) >= dev->sms / 2)
         return launch_pair(stream, a, *dev);
 
     // Tile width: the widest tile that still gives every SM work.

@@ -58,7 +58,7 @@ def _load():
                                              vp, i64, vp, vp, vp]
     lib.pplb200_i8i8_column_parallel_linear.argtypes = [vp, vp, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
                                                         i32, i32, vp, i32, vp, vp, vp, i64, vp]
-    lib.pplb200_i8i8_row_parallel_linear.argtypes = [vp, vp, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
+    lib.pplb200_i8i8_row_parallel_linear.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
                                                      i32, i32, vp, i32, i32, vp, vp, i64, vp]
     lib.pplb200_nccl_get_unique_id.argtypes = [vp]
     lib.pplb200_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
@@ -209,7 +209,7 @@ def row_parallel_linear(xq, w, scale_m, scale_n, bias, in_features, out_features
         out = torch.empty((M, out_features), dtype=torch.float16, device=xq.device)
     if quant_buffer is None and size > 1 and reduce_mode == 0:
         quant_buffer = torch.empty((M, out_features), dtype=torch.int32, device=xq.device)
-    _check(lib.pplb200_i8i8_row_parallel_linear(_stream(), _ptr(xq), M, _ptr(w), _ptr(bias), _ptr(scale_m),
+    _check(lib.pplb200_i8i8_row_parallel_linear(_stream(), _ptr(xq), M, xq.stride(0), _ptr(w), _ptr(bias), _ptr(scale_m),
                                                 _ptr(scale_n), down_m, down_n, in_features, out_features,
                                                 weight_layout, rank, size, comm, 1 if input_is_parallel else 0,
                                                 reduce_mode, _ptr(quant_buffer), None, 0, _ptr(out)))

@@ -1,0 +1,82 @@
+"""Tensor-parallel linears on real GPUs (one process per GPU, NCCL over NVLink), through the C ABI.
+
+Needs >= 2 CUDA devices; skipped otherwise.  Checks, bit for bit, that
+  * the row-parallel linear with the exact int32 reduction equals the unsharded fused linear,
+  * the column-parallel linear with gather_output equals the unsharded fused linear,
+and that the reference-order fp16 reduction stays within a few ulp of the exact result."""
+import os
+import sys
+import time
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, tmp):
+    sys.path.insert(0, os.path.join(ROOT, "ppl.llm.kernel.cuda_b200"))
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    import torch
+    torch.cuda.set_device(rank)
+    import pplb200
+    from pplb200 import workloads as wl
+
+    uid_path = os.path.join(tmp, "uid")
+    if rank == 0:
+        with open(uid_path + ".tmp", "wb") as f:
+            f.write(pplb200.nccl_unique_id())
+        os.rename(uid_path + ".tmp", uid_path)
+    t0 = time.time()
+    while not os.path.exists(uid_path):
+        if time.time() - t0 > 60:
+            raise RuntimeError("rank %d: no NCCL id from rank 0" % rank)
+        time.sleep(0.05)
+    comm = pplb200.nccl_comm_init(open(uid_path, "rb").read(), rank, world)
+
+    rng = np.random.default_rng(123)  # same inputs on every rank
+    results = {}
+    for (M, K, N) in [(64, 1024, 512), (300, 2048, 1536), (1024, 1024, 768), (33, 512, 256)]:  # chunked / odd-M paths too
+        x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float16)).cuda()
+        w = torch.from_numpy(rng.integers(-127, 128, (N, K), dtype=np.int8)).cuda()
+        sn = torch.from_numpy((rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)).cuda()
+        bias = torch.from_numpy((rng.standard_normal(N) * 0.02).astype(np.float16)).cuda()
+        xq, sm = pplb200.minmax_quantize_fp16(x)
+        full = pplb200.row_parallel_linear(xq, w, sm, sn, bias, K, N)  # size 1: unsharded fused linear
+
+        k0, k1 = wl.shard_rows(K, world, rank)
+        y_row = pplb200.row_parallel_linear(xq[:, k0:k1], w[:, k0:k1].contiguous(), sm, sn, bias, K, N,
+                                            rank=rank, size=world, comm=comm)
+        y_ref_order = pplb200.row_parallel_linear(xq[:, k0:k1], w[:, k0:k1].contiguous(), sm, sn, bias, K, N,
+                                                  rank=rank, size=world, comm=comm, reduce_mode=1)
+        n0, n1 = wl.shard_rows(N, world, rank)
+        gather = torch.empty((world, M, n1 - n0), dtype=torch.float16, device="cuda")
+        y_col = pplb200.column_parallel_linear(xq, w[n0:n1].contiguous(), sm, sn[n0:n1].contiguous(),
+                                               bias[n0:n1].contiguous(), K, N, rank=rank, size=world, comm=comm,
+                                               gather_output=True, gather_buffer=gather)
+        torch.cuda.synchronize()
+        key = "%dx%dx%d" % (M, K, N)
+        results[key + " row exact"] = bool(torch.equal(y_row.view(torch.int16), full.view(torch.int16)))
+        results[key + " col gather"] = bool(torch.equal(y_col.view(torch.int16), full.view(torch.int16)))
+        err = (y_ref_order.float() - full.float()).abs().max().item()
+        scale = full.float().abs().max().item()
+        results[key + " fp16-order close"] = bool(err <= 4e-3 * scale + 1e-3)
+    ok = pplb200.gemm_status() == 0
+    pplb200.nccl_comm_destroy(comm)
+    with open(os.path.join(tmp, "rank%d" % rank), "w") as f:
+        f.write(repr((ok, results)))
+
+
+@pytest.mark.parametrize("world", [2])
+def test_tensor_parallel_linears_match_unsharded(cuda, tmp_path, world):
+    if cuda.cuda.device_count() < world:
+        pytest.skip("needs %d GPUs" % world)
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(world, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        ok, results = eval(open(os.path.join(str(tmp_path), "rank%d" % r)).read())
+        assert ok, "GEMM status word set on rank %d" % r
+        bad = [k for k, v in results.items() if not v]
+        assert not bad, "rank %d: %s" % (r, bad)
