@@ -87,6 +87,26 @@ int32_t pplb200_i8i8_gemm(pplb200_stream_t stream, const void* A, int64_t lda, c
                           void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q, void* out_q_scale);
 
 /*
+ * Same result as pplb200_i8i8_gemm with PPLB200_EPI_DEQUANT_F16_REQUANT_I8 (out fp16 [M,N] with
+ * ldc == N, out_q int8 [M,N], out_q_scale fp16 [M]) but WITHOUT a workspace argument and without
+ * allocating anything: the per-row scratch lives in a fixed array inside the library.
+ * This entry point has no counterpart in the reference (whose linears take caller-provided buffers
+ * for everything); it exists for callers that cannot obtain device memory when they need the op --
+ * runtimes that gave all of HBM to their own pool and forbid cudaMalloc afterwards, or code running
+ * where the CUDA allocation calls are not allowed.
+ * Limits and rules: M <= PPLB200_STATIC_SCRATCH_MAX_ROWS (larger M returns RC_INVALID_VALUE); the
+ * array (64 KiB) stays resident on every GPU that loads the library; all calls on a device share
+ * it, so calls whose GPU work overlaps race -- issue them on one stream or order them; the first
+ * call on a device resolves the array's address, so make it before any stream capture starts.
+ */
+#define PPLB200_STATIC_SCRATCH_MAX_ROWS 16384
+int32_t pplb200_i8i8_gemm_requant_static_scratch(pplb200_stream_t stream, const void* A, int64_t lda, const void* B,
+                                                 int64_t ldb, int64_t M, int64_t N, int64_t K,
+                                                 const void* scale_M, const void* scale_N, const void* optional_bias,
+                                                 float down_scale_M, float down_scale_N, float requant_up_scale,
+                                                 void* out, void* out_q, void* out_q_scale);
+
+/*
  * Scratch bytes pplb200_i8i8_linear_fp16 needs (quantized activations, row scales, GEMM scratch).
  */
 int64_t pplb200_i8i8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode);

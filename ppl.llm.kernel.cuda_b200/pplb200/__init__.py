@@ -34,7 +34,9 @@ EXPORTS = [
     "pplb200_i8i8_column_parallel_linear", "pplb200_i8i8_row_parallel_linear",
     "pplb200_nccl_get_unique_id", "pplb200_nccl_comm_init", "pplb200_nccl_comm_destroy",
     "pplb200_i8i8_gemm_status", "pplb200_layout_offset",
+    "pplb200_i8i8_gemm_requant_static_scratch",
 ]
+STATIC_SCRATCH_MAX_ROWS = 16384
 
 
 def _load():
@@ -52,6 +54,8 @@ def _load():
     lib.pplb200_i8i8_gemm_workspace_bytes.restype = i64
     lib.pplb200_i8i8_gemm.argtypes = [vp, vp, i64, vp, i64, i64, i64, i64, i32, vp, vp, vp, f32, f32, f32,
                                       vp, i64, vp, i64, vp, vp]
+    lib.pplb200_i8i8_gemm_requant_static_scratch.argtypes = [vp, vp, i64, vp, i64, i64, i64, i64, vp, vp, vp, f32, f32, f32,
+                                                             vp, vp, vp]
     lib.pplb200_i8i8_linear_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.pplb200_i8i8_linear_workspace_bytes.restype = i64
     lib.pplb200_i8i8_linear_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, f32, f32, f32, i32, f32,
@@ -147,6 +151,23 @@ def gemm_i8i8(a, b, mode=EPI_RAW_I32, scale_m=None, scale_n=None, bias=None, dow
                                  _ptr(scale_n), _ptr(bias), down_m, down_n, requant_up_scale, _ptr(ws),
                                  0 if ws is None else ws.numel(), _ptr(y), y.stride(0), _ptr(yq), _ptr(ys)))
     return y if mode != EPI_DEQUANT_F16_REQUANT_I8 else (y, yq, ys)
+
+
+def gemm_requant_static_scratch(a, b, scale_m, scale_n, bias=None, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE,
+                                requant_up_scale=TOKEN_UP_SCALE, out=None, out_q=None, out_q_scale=None):
+    """GEMM + dequant + per-token re-quantize through the entry point that needs no workspace (its
+    scratch is a fixed array inside the library; M <= STATIC_SCRATCH_MAX_ROWS).  The output tensors
+    are created here only when the caller does not pass them; the C call itself allocates nothing."""
+    import torch
+    M, K = a.shape
+    N = b.shape[0]
+    y = out if out is not None else torch.empty((M, N), dtype=torch.float16, device=a.device)
+    yq = out_q if out_q is not None else torch.empty((M, N), dtype=torch.int8, device=a.device)
+    ys = out_q_scale if out_q_scale is not None else torch.empty((M,), dtype=torch.float16, device=a.device)
+    _check(lib.pplb200_i8i8_gemm_requant_static_scratch(_stream(), _ptr(a), a.stride(0), _ptr(b), b.stride(0), M, N, K,
+                                                        _ptr(scale_m), _ptr(scale_n), _ptr(bias), down_m, down_n,
+                                                        requant_up_scale, _ptr(y), _ptr(yq), _ptr(ys)))
+    return y, yq, ys
 
 
 def linear_workspace_bytes(M, N, K, mode):
