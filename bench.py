@@ -535,12 +535,12 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
-    rank, world = _dist_setup(args.gpus)
-
     if args.impl == "reference":
+        # the reference arm runs on rank 0 alone (no process group is needed); other ranks leave
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
         have_ref = os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libref_i8i8.so"))
-        if rank != 0:
-            return  # the reference arm runs on rank 0 alone
         if not have_ref:
             print(json.dumps(reference_on_cpu(args, args.workload)))
             return
@@ -549,11 +549,15 @@ def main():
         print(json.dumps(line))
         return
 
+    rank, world = _dist_setup(args.gpus)
     sharded = args.workload != "c1"
     line = run_config(args.workload, args, rank, world, "ours", sharded, not args.no_cpu and world == 1)
-    if args.extras:
+    # On more than one GPU the default line (c1 replicas) is accompanied by the two configurations
+    # that really shard: c2 (column parallel, no communication) and c3 (row parallel, int32 reduction).
+    extra_names = ("c0", "c1", "c2", "c3", "c4") if args.extras else (("c2", "c3") if world > 1 and not sharded else ())
+    if extra_names:
         extras = {}
-        for name in ("c0", "c1", "c2", "c3", "c4"):
+        for name in extra_names:
             if name == args.workload:
                 continue
             ex = run_config(name, args, rank, world, "ours", True, False)

@@ -5,12 +5,15 @@
 //   * operands are swapped: 128 weight rows sit on the MMA M axis (TMEM lanes) and the tokens
 //     on the MMA N axis (TMEM columns, BT = 16..128), so no tensor-core work or shared memory is
 //     spent on padding tokens up to 128;
-//   * K is split over a thread-block cluster of S CTAs (one weight-row tile per cluster), sized
-//     so that about two CTAs per SM are resident and all of them stream weights at once;
+//   * one CTA per SM whose whole shared memory is one TMA ring (~200 KB in flight); when there are
+//     fewer weight-row tiles than SMs, K is split over a thread-block cluster of S CTAs (one
+//     weight-row tile per cluster) so that all clusters still fit in one wave;
 //   * the S partial accumulators are combined inside the cluster through distributed shared
 //     memory (a reduce-scatter over 8-column pieces), never through global memory, and each CTA
 //     runs the dequant epilogue for the pieces it owns.  Integer addition makes the result
 //     independent of the split.
+//   * sixteen epilogue warps: a lone warp per scheduler issues well under one instruction per clock,
+//     and the epilogue is not overlapped with anything in a one-tile-per-CTA kernel;
 //   * programmatic dependent launch: weight tiles (which do not depend on the preceding
 //     quantizer kernel) are requested before the kernel waits for its predecessor.
 // Math and operand conventions as in gemm_i8_tcgen05.cu; reference:
@@ -104,6 +107,31 @@ __device__ __forceinline__ void pdl_wait_prior_grid() {
 }
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Per-token maximum over the 32 lanes of a warp for NV tokens held as a[0..NV) in every lane
+// (halving butterfly: NV - 1 shuffles instead of NV full warp reductions).  Returns, in every lane,
+// the maximum for token (lane % NV).
+template <int NV>
+__device__ __forceinline__ uint32_t warp_token_max(uint32_t (&a)[NV], int lane) {
+#pragma unroll
+    for (int off = NV / 2; off >= 1; off >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < off; ++i) {
+            const uint32_t send = upper ? a[i] : a[i + off];
+            const uint32_t keep = upper ? a[i + off] : a[i];
+            const uint32_t got = __shfl_xor_sync(0xffffffffu, send, off);
+            a[i] = keep > got ? keep : got;
+        }
+    }
+    uint32_t r = a[0];
+#pragma unroll
+    for (int off = NV; off < 32; off <<= 1) {
+        const uint32_t got = __shfl_xor_sync(0xffffffffu, r, off);
+        r = r > got ? r : got;
+    }
+    return r;
 }
 
 template <int N> struct TmemLd;
@@ -312,6 +340,9 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         for (int c0 = col_begin; c0 < col_end; c0 += C::LD_COLS) {
             if (c0 >= M) break;
             uint32_t acc[C::LD_COLS];
+            uint32_t absbits[C::LD_COLS]; // |y| as float bits per token column (0 where not owned)
+#pragma unroll
+            for (int j = 0; j < C::LD_COLS; ++j) absbits[j] = 0u;
 
             if (have_acc) {
                 TmemLd<C::LD_COLS>::run(taddr_row + c0, acc);
@@ -360,20 +391,21 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                             if (n_ok && m0 + j < M) dst[(int64_t)j * p.ldc] = h[j];
 #endif
                         if (mode == EPI_DEQUANT_F16_REQUANT_I8) {
-                            // per-token max |y| over this warp's 32 outputs; lane j publishes token j
-                            uint32_t mine = 0u;
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
                                 const float a = n_ok ? fabsf(__half2float(h[j])) : 0.0f;
-                                const uint32_t amax = __reduce_max_sync(0xffffffffu, a == a ? __float_as_uint(a) : 0u);
-                                if (lane == j) mine = amax;
+                                absbits[s8 * 8 + j] = a == a ? __float_as_uint(a) : 0u; // NaNs are dropped, as fmax does
                             }
-                            if (lane < 8 && m0 + lane < M && mine != 0u) atomicMax(&token_absmax[m0 + lane], mine);
                         }
                     }
                 }
                 own += step_rem; slot += step_div;
                 if (own >= S) { own -= S; slot += 1; }
+            }
+            if (mode == EPI_DEQUANT_F16_REQUANT_I8) {
+                // per-token max |y| over this warp's 32 output columns; lane t ends up with token c0 + t
+                const uint32_t tok_max = warp_token_max<C::LD_COLS>(absbits, lane);
+                if (lane < C::LD_COLS && c0 + lane < M && tok_max != 0u) atomicMax(&token_absmax[c0 + lane], tok_max);
             }
         }
     }

@@ -35,18 +35,43 @@ __device__ __forceinline__ float block_max(float v, float* red, int nwarps) {
     return r;
 }
 
-// rn(v / scale) as int, identical to (int)__float2int_rn(__fdiv_rn(v, scale)).
-// v * (1/scale) is within a few ulp of the IEEE quotient, so both round to the same integer
-// unless the product sits next to a half-integer; only then is the exact division issued.
-__device__ __forceinline__ int quant_one(float v, float scale, float inv_scale) {
-    const float t = v * inv_scale;
-    const float n = rintf(t);
-    if (fabsf(fabsf(t - n) - 0.5f) < (1.0f / 4096.0f)) return __float2int_rn(__fdiv_rn(v, scale));
-    return __float2int_rn(t);
-}
-
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+}
+
+// Quantizes 16 consecutive halves to 16 int8 (one 128-bit store): q = rn(v / scale), identical to
+// __float2int_rn(__fdiv_rn(v, scale)).  v * (1/scale) is within a few ulp of the IEEE quotient, so both
+// round to the same integer unless the product sits next to a half-integer.  The "product sits next to a half-integer" test is taken once for the whole group,
+// so the common path is sixteen independent multiply / round chains with no control flow between
+// them; the rare group that contains a near-tie is redone with exact divisions.
+__device__ __forceinline__ uint4 quant16(const __half2* h, float scale, float inv_scale) {
+    float f[16], t[16];
+    bool near_tie = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float2 v = __half22float2(h[i]);
+        f[2 * i] = v.x;
+        f[2 * i + 1] = v.y;
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        t[i] = f[i] * inv_scale;
+        near_tie |= fabsf(fabsf(t[i] - rintf(t[i])) - 0.5f) < (1.0f / 4096.0f);
+    }
+    int qi[16];
+    if (!near_tie) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) qi[i] = __float2int_rn(t[i]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) qi[i] = __float2int_rn(__fdiv_rn(f[i], scale));
+    }
+    uint4 o;
+    o.x = pack4(qi[0], qi[1], qi[2], qi[3]);
+    o.y = pack4(qi[4], qi[5], qi[6], qi[7]);
+    o.z = pack4(qi[8], qi[9], qi[10], qi[11]);
+    o.w = pack4(qi[12], qi[13], qi[14], qi[15]);
+    return o;
 }
 
 // One CTA per row.  A "unit" is 16 consecutive halves (two 128-bit loads, one 128-bit store).
@@ -103,19 +128,7 @@ quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, fl
     for (int u = 0; u < UNITS; ++u) {
         const int unit = unit_base + u * blockDim.x + threadIdx.x;
         if (unit < units) {
-            const __half2* h = reinterpret_cast<const __half2*>(&v[u][0]);
-            int qi[16];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float2 f = __half22float2(h[i]);
-                qi[2 * i] = quant_one(f.x, scale, inv_scale);
-                qi[2 * i + 1] = quant_one(f.y, scale, inv_scale);
-            }
-            uint4 o;
-            o.x = pack4(qi[0], qi[1], qi[2], qi[3]);
-            o.y = pack4(qi[4], qi[5], qi[6], qi[7]);
-            o.z = pack4(qi[8], qi[9], qi[10], qi[11]);
-            o.w = pack4(qi[12], qi[13], qi[14], qi[15]);
+            const uint4 o = quant16(reinterpret_cast<const __half2*>(&v[u][0]), scale, inv_scale);
             const int64_t off = layout_offset(layout, batch, dim, row, (int64_t)unit << 4);
             *reinterpret_cast<uint4*>(q + off) = o;
         }
@@ -155,19 +168,7 @@ quantize_rows_twopass_kernel(const half* __restrict__ in, int64_t batch, int64_t
     const float inv_scale = __frcp_rn(scale);
     for (int64_t unit = threadIdx.x; unit < units; unit += blockDim.x) {
         uint4 a[2] = {src[2 * unit], src[2 * unit + 1]};
-        const __half2* h = reinterpret_cast<const __half2*>(a);
-        int qi[16];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float2 f = __half22float2(h[i]);
-            qi[2 * i] = quant_one(f.x, scale, inv_scale);
-            qi[2 * i + 1] = quant_one(f.y, scale, inv_scale);
-        }
-        uint4 o;
-        o.x = pack4(qi[0], qi[1], qi[2], qi[3]);
-        o.y = pack4(qi[4], qi[5], qi[6], qi[7]);
-        o.z = pack4(qi[8], qi[9], qi[10], qi[11]);
-        o.w = pack4(qi[12], qi[13], qi[14], qi[15]);
+        const uint4 o = quant16(reinterpret_cast<const __half2*>(a), scale, inv_scale);
         *reinterpret_cast<uint4*>(q + layout_offset(layout, batch, dim, row, unit << 4)) = o;
     }
     if (threadIdx.x == 0) {
