@@ -509,6 +509,34 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
     return line
 
 
+def aux_kernels(steps, warmup):
+    """The memory-bound producers timed alone on c4's activation shape (M 8192 x K 8192, 134 MB in,
+    67 MB out: larger than L2): the per-token quantizer and the fused skip + RMSNorm + quantize.
+    Algorithmic bytes: quantizer 3 B per element + 2 B per row; fused producer 7 B per element
+    (input, skip in; skip_out, int8 out) + 2 B per row + the 16 KB weight vector."""
+    import torch
+    import pplb200
+    peaks = _peaks()
+    M, K = 8192, 8192
+    g = torch.Generator(device="cuda").manual_seed(0xB2000004)
+    xs = [torch.randn((M, K), generator=g, device="cuda", dtype=torch.float16) for _ in range(2)]
+    skip = torch.randn((M, K), generator=g, device="cuda", dtype=torch.float16)
+    w = torch.ones((K,), device="cuda", dtype=torch.float16)
+    q = torch.empty((M, K), dtype=torch.int8, device="cuda")
+    sc = torch.empty((M,), dtype=torch.float16, device="cuda")
+    out = {}
+    cases = {
+        "minmax_quantize_fp16": (lambda i: pplb200.minmax_quantize_fp16(xs[i % 2], out=q, scale=sc), 3 * M * K + 2 * M),
+        "skip_rmsnorm_minmax_quantize_fp16": (lambda i: pplb200.skip_rmsnorm_minmax_quantize_fp16(xs[i % 2], w, skip), 7 * M * K + 2 * M + 2 * K),
+    }
+    for name, (fn, nbytes) in cases.items():
+        ms = _time_steps(_Eager(fn), steps, warmup, 1)
+        t = ms / steps * 1e-3
+        out[name] = {"shape": [M, K], "us": t * 1e6, "gb_per_s": nbytes / t / 1e9,
+                     "frac_of_measured_hbm": nbytes / t / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+    return out
+
+
 def reference_on_cpu(args, name):
     """Fallback reference arm when oracle/_ref is absent: the host port of the path."""
     cb = cpu_baseline(name)
@@ -527,6 +555,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1")
     ap.add_argument("--extras", action="store_true", help="also run the other configurations (sharded where they shard)")
+    ap.add_argument("--aux", action="store_true", help="also time the quantizer and the RMSNorm+quantize producer alone")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     args = ap.parse_args()
@@ -565,6 +594,8 @@ def main():
             if "roofline" in ex:
                 extras[name]["roofline"] = ex["roofline"]
         line["other_configs"] = extras
+    if args.aux and rank == 0:
+        line["aux_kernels"] = aux_kernels(args.steps, args.warmup)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:

@@ -49,6 +49,27 @@ inline ppl::common::RetCode minmax_dequantize_fp16(
         down_scale_batch, down_scale_channel, (int32_t)from_layout, output);
 }
 
+// input + skip -> skip_out; quantize(rmsnorm(input + skip) * weight) -> output, output_scale
+// (reference: include/ppl/kernel/llm/cuda/pmx/i8i8/quantize.h:128-141).
+inline ppl::common::RetCode skip_rmsnorm_minmax_quantize_fp16(
+    const cudaStream_t stream,
+    const void* input,            // [batch, hidden dim]
+    const void* weight,           // [hidden dim]
+    const void* skip,             // [batch, hidden dim] or null
+    const float eps,
+    const int64_t batch,
+    const int64_t normalize_shape,
+    const float up_scale,
+    const matrix_layout_t to_layout,
+    void* skip_out,               // [batch, hidden dim]
+    void* output_scale,           // [batch]
+    void* output)                 // [batch, hidden dim]
+{
+    return (ppl::common::RetCode)pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16(
+        (pplb200_stream_t)stream, input, weight, skip, eps, batch, normalize_shape, up_scale, (int32_t)to_layout,
+        skip_out, output_scale, output);
+}
+
 }}}}}}
 
 #endif

@@ -63,6 +63,20 @@ int32_t pplb200_i8i8_minmax_dequantize_fp16(pplb200_stream_t stream, const void*
                                             float down_scale_channel, int32_t from_layout, void* out);
 
 /*
+ * Fused skip-add + RMSNorm + per-token quantize: the producer that feeds the linear in a block.
+ * Replaces ppl::kernel::llm::cuda::pmx::i8i8::skip_rmsnorm_minmax_quantize_fp16
+ *   (include/.../pmx/i8i8/quantize.h:128-141; src/.../pmx/i8i8/rms_norm.cu:40-302).
+ * input, optional_skip fp16 [batch, normalize_shape]; weight fp16 [normalize_shape];
+ * skip_out fp16 [batch, normalize_shape] = input + skip; output int8 in `to_layout` (ROW_MAJOR, COL32,
+ * COL32_2R_4R4); output_scale fp16 [batch] = scale * up_scale.  normalize_shape % 16 == 0, <= 32768.
+ * Rounding: half away from zero with a clamp to +-127, as the reference's quant_scalar.
+ */
+int32_t pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16(pplb200_stream_t stream, const void* input, const void* weight,
+                                                       const void* optional_skip, float eps, int64_t batch,
+                                                       int64_t normalize_shape, float up_scale, int32_t to_layout,
+                                                       void* skip_out, void* output_scale, void* output);
+
+/*
  * Scratch bytes pplb200_i8i8_gemm needs for (M, N, K, mode).  0 means `ws` may be NULL.
  */
 int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode);

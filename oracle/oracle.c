@@ -289,3 +289,48 @@ void orc_sum_partials_i32(const int32_t* const* parts, int32_t nparts, int64_t c
         out[i] = (int32_t)s;
     }
 }
+
+/* ------------------------------------------------------------------ skip + RMSNorm + quantize */
+
+typedef struct {
+    const uint16_t *in, *w, *skip; float eps; int64_t batch, dim; float up; int32_t layout;
+    uint16_t *skip_out, *scale; int8_t* q;
+} rms_ctx;
+
+static void rms_rows(int64_t r0, int64_t r1, void* p) {
+    rms_ctx* c = (rms_ctx*)p;
+    for (int64_t r = r0; r < r1; ++r) {
+        const uint16_t* in = c->in + r * c->dim;
+        uint16_t* z = c->skip_out + r * c->dim;
+        double sumsq = 0.0;
+        float amax = c->eps;                                                /* rms_norm.cu:58 */
+        for (int64_t k = 0; k < c->dim; ++k) {
+            z[k] = c->skip ? orc_f16_add(in[k], c->skip[r * c->dim + k]) : in[k];   /* :62-69 */
+            float x = orc_f16_to_f32(z[k]), w = orc_f16_to_f32(c->w[k]);
+            sumsq += (double)x * (double)x;                                 /* :76 */
+            amax = fmaxf(amax, fabsf(x * w));                               /* :77 */
+        }
+        float mean = (float)sumsq * (1.0f / (float)c->dim);                 /* :86 */
+        float rr = (float)(1.0 / sqrt((double)(mean + c->eps)));            /* :88 rsqrtf */
+        float scale = fmaxf((amax * rr) / (float)127, 1e-7f);               /* :89, quant_utils.h:119-125 */
+        c->scale[r] = orc_f32_to_f16(scale * c->up);                        /* :90 */
+        float inv = 1.0f / scale;                                           /* quant_utils.h:84 */
+        for (int64_t k = 0; k < c->dim; ++k) {
+            float x = orc_f16_to_f32(z[k]), w = orc_f16_to_f32(c->w[k]);
+            float v = ((x * w) * rr) * inv;                                 /* :97, quant_utils.h:84 */
+            int32_t qi = (int32_t)roundf(v);                                /* quant_utils.h:86: half away from zero */
+            qi = qi > 127 ? 127 : (qi < -127 ? -127 : qi);                  /* :87-88 */
+            c->q[orc_layout_offset(c->layout, c->batch, c->dim, r, k)] = (int8_t)qi;
+        }
+    }
+}
+
+int32_t orc_skip_rmsnorm_minmax_quantize_fp16(const uint16_t* input, const uint16_t* weight, const uint16_t* skip,
+                                              float eps, int64_t batch, int64_t dim, float up_scale, int32_t to_layout,
+                                              uint16_t* skip_out, uint16_t* out_scale, int8_t* q) {
+    if (to_layout != ORC_LAYOUT_ROW_MAJOR && to_layout != ORC_LAYOUT_COL32 && to_layout != ORC_LAYOUT_COL32_2R_4R4)
+        return 2;
+    rms_ctx c = { input, weight, skip, eps, batch, dim, up_scale, to_layout, skip_out, out_scale, q };
+    parallel_rows(0, batch, rms_rows, &c);
+    return 0;
+}

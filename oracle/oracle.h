@@ -69,6 +69,16 @@ int32_t orc_w8a8_linear(const uint16_t* x, const int8_t* w, const uint16_t* scal
                         float requant_up_scale,
                         int8_t* xq, uint16_t* sm, int32_t* acc, uint16_t* y, int8_t* yq, uint16_t* yq_scale);
 
+/* pmx/i8i8/rms_norm.cu:40-182 (kernels), :186-302 (launcher); pmx/quant_utils.h:75-92 (quant_scalar).
+ * z = input + skip (fp16 add) -> skip_out; r = 1/sqrt(mean(z^2) + eps); amax = max(eps, max|z*w|);
+ * scale = max(amax * r / 127, 1e-7); q = clamp(round_half_away((z*w*r) * (1/scale)), -127, 127).
+ * The sum of squares is taken in double and the reciprocal square root exactly, whereas the device
+ * kernels sum in fp32 (order unspecified) and use the approximate rsqrtf: compare with tolerance
+ * (scale within 1 fp16 ulp, int8 within 1).  Returns 0, or 2 (unsupported layout). */
+int32_t orc_skip_rmsnorm_minmax_quantize_fp16(const uint16_t* input, const uint16_t* weight, const uint16_t* skip,
+                                              float eps, int64_t batch, int64_t dim, float up_scale, int32_t to_layout,
+                                              uint16_t* skip_out, uint16_t* out_scale, int8_t* q);
+
 /* Elementwise sum of `parts` int32 partial accumulators (row-parallel reduction, exact). */
 void orc_sum_partials_i32(const int32_t* const* parts, int32_t nparts, int64_t count, int32_t* out);
 

@@ -59,6 +59,13 @@ int32_t ref_minmax_dequantize_fp16(cudaStream_t stream, const void* acc, const v
                                                              (refns::matrix_layout_t)layout, out);
 }
 
+int32_t ref_skip_rmsnorm_minmax_quantize_fp16(cudaStream_t stream, const void* in, const void* weight, const void* skip,
+                                              float eps, int64_t batch, int64_t dim, float up_scale, int32_t layout,
+                                              void* skip_out, void* out_scale, void* out) {
+    return (int32_t)refns::pmx::i8i8::skip_rmsnorm_minmax_quantize_fp16(stream, in, weight, skip, eps, batch, dim, up_scale,
+                                                                        (refns::matrix_layout_t)layout, skip_out, out_scale, out);
+}
+
 // C[M,N] i32 = A[M,K] i8 * B[N,K]^T i8 through the reference's cuBLASLt wrapper
 // (first call per shape bucket runs its autotuner, which synchronises the host).
 int32_t ref_gemm_i8i8i32(cudaStream_t stream, const void* A, const void* B, int64_t M, int64_t N, int64_t K,

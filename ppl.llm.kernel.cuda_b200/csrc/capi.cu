@@ -132,6 +132,27 @@ int32_t pplb200_i8i8_minmax_dequantize_fp16(pplb200_stream_t stream, const void*
                              down_scale_batch, down_scale_channel, from_layout, (half*)out);
 }
 
+int32_t pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16(pplb200_stream_t stream, const void* input, const void* weight,
+                                                       const void* optional_skip, float eps, int64_t batch,
+                                                       int64_t normalize_shape, float up_scale, int32_t to_layout,
+                                                       void* skip_out, void* output_scale, void* output) {
+    if (to_layout != LAYOUT_ROW_MAJOR && to_layout != LAYOUT_COL32 && to_layout != LAYOUT_COL32_2R_4R4)
+        return fail(RC_UNSUPPORTED, "unsupported matrix layout: %d", to_layout);
+    if (batch < 0 || normalize_shape < 0) return fail(RC_INVALID_VALUE, "negative extent");
+    if (batch == 0 || normalize_shape == 0) return RC_SUCCESS;
+    if (normalize_shape % 16) return fail(RC_INVALID_VALUE, "normalize_shape must be a multiple of 16, got %lld", (long long)normalize_shape);
+    if (to_layout != LAYOUT_ROW_MAJOR && normalize_shape % 32) return fail(RC_INVALID_VALUE, "COL32 layouts need normalize_shape %% 32 == 0");
+    if (to_layout == LAYOUT_COL32_2R_4R4 && batch % 32) return fail(RC_INVALID_VALUE, "COL32_2R_4R4 needs batch %% 32 == 0");
+    if (!input || !weight || !skip_out || !output_scale || !output) return fail(RC_INVALID_VALUE, "null pointer");
+    if (!aligned16(input) || !aligned16(weight) || !aligned16(skip_out) || !aligned16(output) ||
+        (optional_skip && !aligned16(optional_skip)))
+        return fail(RC_INVALID_VALUE, "input, weight, skip, skip_out and output must be 16-byte aligned");
+    if (batch > 0x7fffffffLL) return fail(RC_UNSUPPORTED, "batch beyond 2^31 - 1");
+    return launch_skip_rmsnorm_quantize((cudaStream_t)stream, (const half*)input, (const half*)weight, (const half*)optional_skip,
+                                        eps, batch, normalize_shape, up_scale, to_layout, (half*)skip_out,
+                                        (half*)output_scale, (int8_t*)output);
+}
+
 int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode) {
     (void)N; (void)K;
     return gemm_ws_bytes(M, epilogue_mode);

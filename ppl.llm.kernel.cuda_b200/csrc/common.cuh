@@ -76,6 +76,10 @@ int32_t launch_dequantize(cudaStream_t stream, const int32_t* acc, const half* b
                           const half* scale_n, int64_t batch, int64_t dim, float down_m, float down_n,
                           int32_t layout, half* out);
 
+int32_t launch_skip_rmsnorm_quantize(cudaStream_t stream, const half* input, const half* weight, const half* skip,
+                                     float eps, int64_t batch, int64_t dim, float up_scale, int32_t layout,
+                                     half* skip_out, half* scale_out, int8_t* q);
+
 int32_t launch_transpose01_f16(cudaStream_t stream, const half* in, int64_t d0, int64_t d1, int64_t d2, half* out);
 
 struct GemmArgs {

@@ -34,7 +34,7 @@ EXPORTS = [
     "pplb200_i8i8_column_parallel_linear", "pplb200_i8i8_row_parallel_linear",
     "pplb200_nccl_get_unique_id", "pplb200_nccl_comm_init", "pplb200_nccl_comm_destroy",
     "pplb200_i8i8_gemm_status", "pplb200_layout_offset",
-    "pplb200_i8i8_gemm_requant_static_scratch",
+    "pplb200_i8i8_gemm_requant_static_scratch", "pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -49,6 +49,7 @@ def _load():
     lib.pplb200_version.restype = ctypes.c_char_p
     lib.pplb200_last_error.restype = ctypes.c_char_p
     lib.pplb200_i8i8_minmax_quantize_fp16.argtypes = [vp, vp, i64, i64, f32, i32, vp, vp]
+    lib.pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16.argtypes = [vp, vp, vp, vp, f32, i64, i64, f32, i32, vp, vp, vp]
     lib.pplb200_i8i8_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
     lib.pplb200_i8i8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.pplb200_i8i8_gemm_workspace_bytes.restype = i64
@@ -116,6 +117,19 @@ def minmax_quantize_fp16(x, up_scale=TOKEN_UP_SCALE, to_layout=MATRIX_LAYOUT_ROW
     s = scale if scale is not None else torch.empty((batch,), dtype=torch.float16, device=x.device)
     _check(lib.pplb200_i8i8_minmax_quantize_fp16(_stream(), _ptr(x), batch, dim, up_scale, to_layout, _ptr(q), _ptr(s)))
     return q, s
+
+
+def skip_rmsnorm_minmax_quantize_fp16(x, weight, skip=None, eps=1e-5, up_scale=TOKEN_UP_SCALE,
+                                      to_layout=MATRIX_LAYOUT_ROW_MAJOR):
+    """x (+ skip) fp16 [batch, dim], weight fp16 [dim] -> (skip_out fp16, q int8, scale fp16 [batch])."""
+    import torch
+    batch, dim = x.shape
+    skip_out = torch.empty_like(x)
+    q = torch.empty((batch, dim), dtype=torch.int8, device=x.device)
+    s = torch.empty((batch,), dtype=torch.float16, device=x.device)
+    _check(lib.pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16(_stream(), _ptr(x), _ptr(weight), _ptr(skip), eps, batch, dim,
+                                                              up_scale, to_layout, _ptr(skip_out), _ptr(s), _ptr(q)))
+    return skip_out, q, s
 
 
 def minmax_dequantize_fp16(acc, scale_m, scale_n, bias=None, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE,

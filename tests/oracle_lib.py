@@ -38,6 +38,7 @@ def _load():
     L.orc_gemm_i8i8i32_rows.argtypes = [vp, i64, vp, i64, i64, i64, i64, i64, vp, i64]
     L.orc_gemm_i8i8i32_rows.restype = None
     L.orc_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
+    L.orc_skip_rmsnorm_minmax_quantize_fp16.argtypes = [vp, vp, vp, f32, i64, i64, f32, i32, vp, vp, vp]
     L.orc_w8a8_linear.argtypes = [vp, vp, vp, vp, i64, i64, i64, f32, f32, f32, f32, vp, vp, vp, vp, vp, vp]
     return L
 
@@ -120,6 +121,18 @@ def linear(x, w, scale_n, bias=None, requant=False, up_scale=TOKEN_UP, down_m=TO
     return r
 
 
+def skip_rmsnorm_quantize(x, weight, skip=None, eps=1e-5, up_scale=TOKEN_UP, layout=ROW_MAJOR):
+    """Returns (rc, skip_out float16 [M,K], q int8 [M,K], scale float16 [M])."""
+    x, weight = _c(x, np.float16), _c(weight, np.float16)
+    M, K = x.shape
+    z = np.empty((M, K), np.float16)
+    q = np.zeros((M, K), np.int8)
+    s = np.empty((M,), np.float16)
+    rc = L.orc_skip_rmsnorm_minmax_quantize_fp16(_p(x), _p(weight), _p(None if skip is None else _c(skip, np.float16)), eps,
+                                                 M, K, up_scale, layout, _p(z), _p(s), _p(q))
+    return rc, z, q, s
+
+
 def layout_offset(layout, rows, cols, r, c):
     return L.orc_layout_offset(layout, rows, cols, r, c)
 
@@ -127,10 +140,6 @@ def layout_offset(layout, rows, cols, r, c):
 def to_layout(mat, layout):
     """Row-major numpy matrix -> flat array in `layout` (rows/cols padded as the layout needs)."""
     rows, cols = mat.shape
-    size = 0
-    for r in (0, rows - 1):
-        for c in (0, cols - 1):
-            pass
     idx = np.empty((rows, cols), dtype=np.int64)
     for r in range(rows):
         for c in range(cols):

@@ -189,3 +189,25 @@ def test_layout_offsets_are_bijections(oracle, layout):
     _, idx = oracle.to_layout(np.zeros((rows, cols), np.int8), layout)
     flat = idx.ravel()
     assert len(np.unique(flat)) == rows * cols and flat.min() == 0 and flat.max() == rows * cols - 1
+
+
+def test_skip_rmsnorm_quantize_vs_numpy(oracle):
+    rng = np.random.default_rng(8)
+    M, K = 9, 320
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    skip = (rng.standard_normal((M, K)) * 0.5).astype(np.float16)
+    w = (1.0 + 0.2 * rng.standard_normal(K)).astype(np.float16)
+    rc, z, q, s = oracle.skip_rmsnorm_quantize(x, w, skip, eps=1e-5)
+    assert rc == 0
+    zn = (x.astype(np.float64) + skip.astype(np.float64)).astype(np.float16)
+    assert np.array_equal(bits(z), bits(zn))
+    zf, wf = zn.astype(np.float32), w.astype(np.float32)
+    mean = ((zf.astype(np.float64) ** 2).sum(axis=1)).astype(np.float32) * np.float32(1.0 / K)
+    r = (1.0 / np.sqrt((mean + np.float32(1e-5)).astype(np.float64))).astype(np.float32)
+    amax = np.maximum(np.float32(1e-5), np.abs(zf * wf).max(axis=1))
+    scale = np.maximum((amax * r) / np.float32(127), np.float32(1e-7)).astype(np.float32)
+    v = ((zf * wf) * r[:, None]).astype(np.float32) * (np.float32(1) / scale)[:, None]
+    qn = np.clip(np.sign(v) * np.floor(np.abs(v) + np.float32(0.5)), -127, 127).astype(np.int8)
+    assert np.array_equal(q, qn)
+    assert np.array_equal(bits(s), bits((scale * np.float32(4096)).astype(np.float16)))
+    assert oracle.skip_rmsnorm_quantize(x, w, skip, layout=1)[0] == 2

@@ -69,7 +69,7 @@ def _worker(rank, world, tmp):
         f.write(repr((ok, results)))
 
 
-@pytest.mark.parametrize("world", [2])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_tensor_parallel_linears_match_unsharded(cuda, tmp_path, world):
     if cuda.cuda.device_count() < world:
         pytest.skip("needs %d GPUs" % world)
