@@ -16,8 +16,8 @@ constexpr int QTPB = 256;
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
     uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
 
@@ -35,18 +35,18 @@ __device__ __forceinline__ float block_max(float v, float* red, int nwarps) {
     return r;
 }
 
-__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
-}
-
 // Quantizes 16 consecutive halves to 16 int8 (one 128-bit store): q = rn(v / scale), identical to
 // __float2int_rn(__fdiv_rn(v, scale)).  v * (1/scale) is within a few ulp of the IEEE quotient, so both
-// round to the same integer unless the product sits next to a half-integer.  The "product sits next to a half-integer" test is taken once for the whole group,
-// so the common path is sixteen independent multiply / round chains with no control flow between
-// them; the rare group that contains a near-tie is redone with exact divisions.
+// round to the same integer unless the product sits next to a half-integer.  The common path uses
+// only full-rate arithmetic: adding 1.5 * 2^23 rounds the product to the nearest-even integer and
+// leaves that integer's two's-complement byte in the low mantissa bits; subtracting it back gives
+// the rounding residual, and the group is redone with exact divisions only if some residual is
+// within 2^-12 of one half (or is not a number: NaN / infinite inputs take the exact path too).
 __device__ __forceinline__ uint4 quant16(const __half2* h, float scale, float inv_scale) {
-    float f[16], t[16];
-    bool near_tie = false;
+    constexpr float kMagic = 12582912.0f; // 1.5 * 2^23
+    float f[16];
+    uint32_t b[16];
+    bool safe = true;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const float2 v = __half22float2(h[i]);
@@ -55,22 +55,21 @@ __device__ __forceinline__ uint4 quant16(const __half2* h, float scale, float in
     }
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
-        t[i] = f[i] * inv_scale;
-        near_tie |= fabsf(fabsf(t[i] - rintf(t[i])) - 0.5f) < (1.0f / 4096.0f);
+        const float t = f[i] * inv_scale;
+        const float u = __fadd_rn(t, kMagic);
+        const float resid = __fsub_rn(t, __fsub_rn(u, kMagic));
+        b[i] = __float_as_uint(u);
+        safe = safe && (fabsf(resid) < 0.5f - 1.0f / 4096.0f);
     }
-    int qi[16];
-    if (!near_tie) {
+    if (!safe) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) qi[i] = __float2int_rn(t[i]);
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) qi[i] = __float2int_rn(__fdiv_rn(f[i], scale));
+        for (int i = 0; i < 16; ++i) b[i] = (uint32_t)__float2int_rn(__fdiv_rn(f[i], scale));
     }
     uint4 o;
-    o.x = pack4(qi[0], qi[1], qi[2], qi[3]);
-    o.y = pack4(qi[4], qi[5], qi[6], qi[7]);
-    o.z = pack4(qi[8], qi[9], qi[10], qi[11]);
-    o.w = pack4(qi[12], qi[13], qi[14], qi[15]);
+    o.x = __byte_perm(__byte_perm(b[0], b[1], 0x0040), __byte_perm(b[2], b[3], 0x0040), 0x5410);
+    o.y = __byte_perm(__byte_perm(b[4], b[5], 0x0040), __byte_perm(b[6], b[7], 0x0040), 0x5410);
+    o.z = __byte_perm(__byte_perm(b[8], b[9], 0x0040), __byte_perm(b[10], b[11], 0x0040), 0x5410);
+    o.w = __byte_perm(__byte_perm(b[12], b[13], 0x0040), __byte_perm(b[14], b[15], 0x0040), 0x5410);
     return o;
 }
 
