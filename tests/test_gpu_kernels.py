@@ -45,6 +45,30 @@ def test_quantize_rowmajor(cuda, oracle, M, K, kind):
     assert np.array_equal(q.cpu().numpy(), q_ref)
 
 
+@pytest.mark.parametrize("M,K", [(600, 512), (1200, 4096), (700, 8192), (640, 28672), (2000, 48), (593, 51200)])
+@pytest.mark.parametrize("kind", ["normal", "ties", "wide"])
+def test_quantize_large_batch(cuda, oracle, M, K, kind):
+    """Several rows per SM, including row lengths at the edge of the register-resident kernel."""
+    import pplb200
+    rng = np.random.default_rng(M + K)
+    x = _rand_x(rng, M, K, kind)
+    rc, q_ref, s_ref = oracle.quantize(x)
+    q, s = pplb200.minmax_quantize_fp16(_t(cuda, x))
+    cuda.cuda.synchronize()
+    assert np.array_equal(oracle.f16_bits(s.cpu().numpy()), oracle.f16_bits(s_ref))
+    assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
+def test_quantize_large_batch_col32(cuda, oracle):
+    import pplb200
+    rng = np.random.default_rng(11)
+    x = _rand_x(rng, 640, 256, "normal")
+    for layout in (2, 3):
+        q_ref = oracle.quantize(x, layout=layout)[1]
+        q, _ = pplb200.minmax_quantize_fp16(_t(cuda, x), to_layout=layout)
+        assert np.array_equal(q.cpu().numpy(), q_ref)
+
+
 @pytest.mark.parametrize("layout", [2, 3])
 def test_quantize_col32_layouts(cuda, oracle, layout):
     import pplb200
