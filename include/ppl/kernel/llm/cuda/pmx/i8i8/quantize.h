@@ -49,6 +49,51 @@ inline ppl::common::RetCode minmax_dequantize_fp16(
         down_scale_batch, down_scale_channel, (int32_t)from_layout, output);
 }
 
+// Consumers of the raw int32 GEMM output; reference declarations quantize.h:57-126.
+inline ppl::common::RetCode minmax_dequantize_split3_fp16(
+    cudaStream_t stream, const void* input, const void* optional_bias, const void* scale_per_batch,
+    const void* scale_per_channel, const int64_t batch, const int64_t quant_dim, const int64_t split_dim_0,
+    const int64_t split_dim_1, const int64_t split_dim_2, const float down_scale_batch, const float down_scale_channel,
+    const matrix_layout_t from_layout, void* output_0, void* output_1, void* output_2)
+{
+    return (ppl::common::RetCode)pplb200_i8i8_minmax_dequantize_split3_fp16(
+        (pplb200_stream_t)stream, input, optional_bias, scale_per_batch, scale_per_channel, batch, quant_dim, split_dim_0,
+        split_dim_1, split_dim_2, down_scale_batch, down_scale_channel, (int32_t)from_layout, output_0, output_1, output_2);
+}
+
+inline ppl::common::RetCode minmax_dequantize_silu_fp16(
+    cudaStream_t stream, const void* input, const void* input_scale_per_batch, const void* input_scale_per_channel,
+    const void* optional_gate, const void* gate_scale_per_batch, const void* gate_scale_per_channel, const int64_t batch,
+    const int64_t quant_dim, const matrix_layout_t from_layout, float down_scale_batch, float down_scale_channel,
+    void* output)
+{
+    return (ppl::common::RetCode)pplb200_i8i8_minmax_dequantize_silu_fp16(
+        (pplb200_stream_t)stream, input, input_scale_per_batch, input_scale_per_channel, optional_gate, gate_scale_per_batch,
+        gate_scale_per_channel, batch, quant_dim, (int32_t)from_layout, down_scale_batch, down_scale_channel, output);
+}
+
+inline ppl::common::RetCode minmax_requantize_silu_fp16(
+    cudaStream_t stream, const void* input, const void* input_scale_per_batch, const void* input_scale_per_channel,
+    const void* optional_gate, const void* gate_scale_per_batch, const void* gate_scale_per_channel, const int64_t batch,
+    const int64_t quant_dim, const matrix_layout_t layout, const float up_scale, const float down_scale_batch,
+    const float down_scale_channel, void* workspace, void* output, void* scale)
+{
+    return (ppl::common::RetCode)pplb200_i8i8_minmax_requantize_silu_fp16(
+        (pplb200_stream_t)stream, input, input_scale_per_batch, input_scale_per_channel, optional_gate, gate_scale_per_batch,
+        gate_scale_per_channel, batch, quant_dim, (int32_t)layout, up_scale, down_scale_batch, down_scale_channel, workspace,
+        output, scale);
+}
+
+inline ppl::common::RetCode minmax_requantize_swiglu_fp16(
+    cudaStream_t stream, const void* input, const void* input_scale_per_batch, const void* input_scale_per_channel,
+    const int64_t batch, const int64_t quant_dim, const float beta, const matrix_layout_t layout, const float up_scale,
+    const float down_scale_batch, const float down_scale_channel, void* workspace, void* output, void* scale)
+{
+    return (ppl::common::RetCode)pplb200_i8i8_minmax_requantize_swiglu_fp16(
+        (pplb200_stream_t)stream, input, input_scale_per_batch, input_scale_per_channel, batch, quant_dim, beta,
+        (int32_t)layout, up_scale, down_scale_batch, down_scale_channel, workspace, output, scale);
+}
+
 // input + skip -> skip_out; quantize(rmsnorm(input + skip) * weight) -> output, output_scale
 // (reference: include/ppl/kernel/llm/cuda/pmx/i8i8/quantize.h:128-141).
 inline ppl::common::RetCode skip_rmsnorm_minmax_quantize_fp16(

@@ -77,6 +77,40 @@ int32_t pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16(pplb200_stream_t stream, 
                                                        void* skip_out, void* output_scale, void* output);
 
 /*
+ * Consumers of the raw int32 accumulators (column_parallel_linear with gather_output == 0).
+ * Replace, with the same argument meaning,
+ *   minmax_dequantize_split3_fp16   (include/.../pmx/i8i8/quantize.h:57-74;  src/.../pmx/i8i8/split.cu:44-169)
+ *   minmax_dequantize_silu_fp16     (quantize.h:76-90; declared by the reference, defined nowhere in it)
+ *   minmax_requantize_silu_fp16     (quantize.h:92-109; src/.../pmx/i8i8/silu.cu:44-199)
+ *   minmax_requantize_swiglu_fp16   (quantize.h:111-126; src/.../pmx/i8i8/swiglu.cu:42-185)
+ * input int32 [batch, quant_dim] (SwiGLU: [batch, 2 * quant_dim] = [x | gate], channel scales [2 * quant_dim]).
+ * Activations: layouts ROW_MAJOR, COL32, COL32_2R_4R4; quant_dim % 16 == 0 and <= 32768; `workspace`
+ * receives the fp16 activated values (may be NULL), `output` int8 and `scale` fp16 [batch] = scale * up_scale.
+ * split3: any of the five layouts, quant_dim and the three split sizes multiples of 4.
+ */
+int32_t pplb200_i8i8_minmax_dequantize_split3_fp16(pplb200_stream_t stream, const void* input, const void* optional_bias,
+                                                   const void* scale_per_batch, const void* scale_per_channel,
+                                                   int64_t batch, int64_t quant_dim, int64_t split_dim_0,
+                                                   int64_t split_dim_1, int64_t split_dim_2, float down_scale_batch,
+                                                   float down_scale_channel, int32_t from_layout, void* output_0,
+                                                   void* output_1, void* output_2);
+int32_t pplb200_i8i8_minmax_dequantize_silu_fp16(pplb200_stream_t stream, const void* input, const void* input_scale_per_batch,
+                                                 const void* input_scale_per_channel, const void* optional_gate,
+                                                 const void* gate_scale_per_batch, const void* gate_scale_per_channel,
+                                                 int64_t batch, int64_t quant_dim, int32_t from_layout,
+                                                 float down_scale_batch, float down_scale_channel, void* output);
+int32_t pplb200_i8i8_minmax_requantize_silu_fp16(pplb200_stream_t stream, const void* input, const void* input_scale_per_batch,
+                                                 const void* input_scale_per_channel, const void* optional_gate,
+                                                 const void* gate_scale_per_batch, const void* gate_scale_per_channel,
+                                                 int64_t batch, int64_t quant_dim, int32_t layout, float up_scale,
+                                                 float down_scale_batch, float down_scale_channel, void* workspace,
+                                                 void* output, void* scale);
+int32_t pplb200_i8i8_minmax_requantize_swiglu_fp16(pplb200_stream_t stream, const void* input, const void* input_scale_per_batch,
+                                                   const void* input_scale_per_channel, int64_t batch, int64_t quant_dim,
+                                                   float beta, int32_t layout, float up_scale, float down_scale_batch,
+                                                   float down_scale_channel, void* workspace, void* output, void* scale);
+
+/*
  * Scratch bytes pplb200_i8i8_gemm needs for (M, N, K, mode).  0 means `ws` may be NULL.
  */
 int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode);

@@ -334,3 +334,63 @@ int32_t orc_skip_rmsnorm_minmax_quantize_fp16(const uint16_t* input, const uint1
     parallel_rows(0, batch, rms_rows, &c);
     return 0;
 }
+
+/* ------------------------------------------------------------------ activation consumers */
+
+int32_t orc_activation_requantize(int32_t kind, const int32_t* input, const uint16_t* scale_b, const uint16_t* scale_c,
+                                  const int32_t* gate, const uint16_t* gate_scale_b, const uint16_t* gate_scale_c,
+                                  int64_t batch, int64_t dim, float beta, float up_scale, float down_b, float down_c,
+                                  uint16_t* workspace, int8_t* out_q, uint16_t* out_scale) {
+    if (kind < 0 || kind > 2) return 2;
+    const int64_t in_cols = kind == 2 ? 2 * dim : dim;
+    for (int64_t r = 0; r < batch; ++r) {
+        float bs = orc_f16_to_f32(scale_b[r]) * down_b;                                   /* silu.cu:68, swiglu.cu:67 */
+        float gs = kind == 1 ? orc_f16_to_f32(gate_scale_b[r]) * down_b : 0.0f;           /* silu.cu:69 */
+        float lmax = 0.0f;
+        for (int64_t i = 0; i < dim; ++i) {
+            float v = (float)input[r * in_cols + i] * orc_f16_to_f32(scale_c[i]);         /* silu.cu:95, swiglu.cu:92 */
+            v = v * down_c; v = v * bs;
+            if (kind == 2) {
+                float g = (float)input[r * in_cols + dim + i] * orc_f16_to_f32(scale_c[dim + i]);
+                g = g * down_c; g = g * bs;                                               /* swiglu.cu:93 */
+                v = (v / (1.0f + expf(-v * beta))) * g;                                   /* swiglu.cu:96 */
+            } else {
+                v = v / (1.0f + expf(-v));                                                /* silu.cu:98 */
+                if (kind == 1) {
+                    float g = (float)gate[r * dim + i] * orc_f16_to_f32(gate_scale_c[i]); /* silu.cu:101 */
+                    g = g * down_c; g = g * gs;
+                    v = v * g;
+                }
+            }
+            workspace[r * dim + i] = orc_f32_to_f16(v);                                   /* silu.cu:104 */
+            lmax = fmaxf(fabsf(v), lmax);                                                 /* silu.cu:105 */
+        }
+        if (out_q && out_scale) {
+            float scale = fmaxf(lmax / (float)127, 1e-7f);                                /* silu.cu:112 */
+            out_scale[r] = orc_f32_to_f16(scale * up_scale);                              /* silu.cu:114 */
+            for (int64_t i = 0; i < dim; ++i)                                             /* silu.cu:127 */
+                out_q[r * dim + i] = (int8_t)float2int_rn(orc_f16_to_f32(workspace[r * dim + i]) / scale);
+        }
+    }
+    return 0;
+}
+
+int32_t orc_dequantize_split3(const int32_t* acc, const uint16_t* bias, const uint16_t* scale_m, const uint16_t* scale_n,
+                              int64_t batch, int64_t dim, int64_t d0, int64_t d1, int64_t d2, float down_m, float down_n,
+                              uint16_t* o0, uint16_t* o1, uint16_t* o2) {
+    if (dim % 4 != 0) return 4;
+    for (int64_t m = 0; m < batch; ++m) {
+        float bs = orc_f16_to_f32(scale_m[m]) * down_m;
+        for (int64_t n = 0; n < dim; ++n) {
+            float t = (float)acc[m * dim + n] * orc_f16_to_f32(scale_n[n]);
+            t = t * down_n; t = t * bs;
+            uint16_t h = orc_f32_to_f16(t);
+            if (bias) h = orc_f16_add(h, bias[n]);
+            int64_t g = n & ~(int64_t)3;                     /* split.cu:73-79: a 4-column group goes where its first column goes */
+            if (g < d0) o0[m * d0 + n] = h;
+            else if (g < d0 + d1) o1[m * d1 + (n - d0)] = h;
+            else if (g < d0 + d1 + d2) o2[m * d2 + (n - d0 - d1)] = h;
+        }
+    }
+    return 0;
+}

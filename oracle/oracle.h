@@ -79,6 +79,21 @@ int32_t orc_skip_rmsnorm_minmax_quantize_fp16(const uint16_t* input, const uint1
                                               float eps, int64_t batch, int64_t dim, float up_scale, int32_t to_layout,
                                               uint16_t* skip_out, uint16_t* out_scale, int8_t* q);
 
+/* pmx/i8i8/silu.cu:44-133 / swiglu.cu:42-128: dequantize -> SiLU [x gate] or SwiGLU -> fp16 workspace;
+ * row max of the fp32 value before rounding; q = rn(float(fp16) / scale).  kind 0 SiLU, 1 gated SiLU
+ * (gate int32 [batch, dim] with its own scales), 2 SwiGLU (input [batch, 2 dim] = [x | gate], channel
+ * scales [2 dim]).  expf is exact here, the device uses __expf: compare with tolerance.  out_q / out_scale
+ * may be NULL (dequantize + activation only).  Row-major only. */
+int32_t orc_activation_requantize(int32_t kind, const int32_t* input, const uint16_t* scale_b, const uint16_t* scale_c,
+                                  const int32_t* gate, const uint16_t* gate_scale_b, const uint16_t* gate_scale_c,
+                                  int64_t batch, int64_t dim, float beta, float up_scale, float down_b, float down_c,
+                                  uint16_t* workspace, int8_t* out_q, uint16_t* out_scale);
+
+/* pmx/i8i8/split.cu:44-84: dequantize (+bias) and route 4-column groups to three row-major outputs. */
+int32_t orc_dequantize_split3(const int32_t* acc, const uint16_t* bias, const uint16_t* scale_m, const uint16_t* scale_n,
+                              int64_t batch, int64_t dim, int64_t d0, int64_t d1, int64_t d2, float down_m, float down_n,
+                              uint16_t* o0, uint16_t* o1, uint16_t* o2);
+
 /* Elementwise sum of `parts` int32 partial accumulators (row-parallel reduction, exact). */
 void orc_sum_partials_i32(const int32_t* const* parts, int32_t nparts, int64_t count, int32_t* out);
 

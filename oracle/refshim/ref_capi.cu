@@ -66,6 +66,27 @@ int32_t ref_skip_rmsnorm_minmax_quantize_fp16(cudaStream_t stream, const void* i
                                                                         (refns::matrix_layout_t)layout, skip_out, out_scale, out);
 }
 
+int32_t ref_minmax_dequantize_split3_fp16(cudaStream_t stream, const void* in, const void* bias, const void* sb, const void* sc,
+                                          int64_t batch, int64_t dim, int64_t d0, int64_t d1, int64_t d2, float down_b,
+                                          float down_c, int32_t layout, void* o0, void* o1, void* o2) {
+    return (int32_t)refns::pmx::i8i8::minmax_dequantize_split3_fp16(stream, in, bias, sb, sc, batch, dim, d0, d1, d2, down_b, down_c,
+                                                                    (refns::matrix_layout_t)layout, o0, o1, o2);
+}
+
+int32_t ref_minmax_requantize_silu_fp16(cudaStream_t stream, const void* in, const void* sb, const void* sc, const void* gate,
+                                        const void* gsb, const void* gsc, int64_t batch, int64_t dim, int32_t layout,
+                                        float up, float down_b, float down_c, void* ws, void* out, void* scale) {
+    return (int32_t)refns::pmx::i8i8::minmax_requantize_silu_fp16(stream, in, sb, sc, gate, gsb, gsc, batch, dim,
+                                                                  (refns::matrix_layout_t)layout, up, down_b, down_c, ws, out, scale);
+}
+
+int32_t ref_minmax_requantize_swiglu_fp16(cudaStream_t stream, const void* in, const void* sb, const void* sc, int64_t batch,
+                                          int64_t dim, float beta, int32_t layout, float up, float down_b, float down_c,
+                                          void* ws, void* out, void* scale) {
+    return (int32_t)refns::pmx::i8i8::minmax_requantize_swiglu_fp16(stream, in, sb, sc, batch, dim, beta,
+                                                                    (refns::matrix_layout_t)layout, up, down_b, down_c, ws, out, scale);
+}
+
 // C[M,N] i32 = A[M,K] i8 * B[N,K]^T i8 through the reference's cuBLASLt wrapper
 // (first call per shape bucket runs its autotuner, which synchronises the host).
 int32_t ref_gemm_i8i8i32(cudaStream_t stream, const void* A, const void* B, int64_t M, int64_t N, int64_t K,

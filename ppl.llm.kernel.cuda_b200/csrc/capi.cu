@@ -153,6 +153,46 @@ int32_t pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16(pplb200_stream_t stream, 
                                         (half*)output_scale, (int8_t*)output);
 }
 
+int32_t pplb200_i8i8_minmax_dequantize_split3_fp16(pplb200_stream_t stream, const void* input, const void* optional_bias,
+                                                   const void* scale_per_batch, const void* scale_per_channel,
+                                                   int64_t batch, int64_t quant_dim, int64_t split_dim_0,
+                                                   int64_t split_dim_1, int64_t split_dim_2, float down_scale_batch,
+                                                   float down_scale_channel, int32_t from_layout, void* output_0,
+                                                   void* output_1, void* output_2) {
+    return dequantize_split3((cudaStream_t)stream, input, optional_bias, scale_per_batch, scale_per_channel, batch, quant_dim,
+                             split_dim_0, split_dim_1, split_dim_2, down_scale_batch, down_scale_channel, from_layout,
+                             output_0, output_1, output_2);
+}
+
+int32_t pplb200_i8i8_minmax_dequantize_silu_fp16(pplb200_stream_t stream, const void* input, const void* input_scale_per_batch,
+                                                 const void* input_scale_per_channel, const void* optional_gate,
+                                                 const void* gate_scale_per_batch, const void* gate_scale_per_channel,
+                                                 int64_t batch, int64_t quant_dim, int32_t from_layout,
+                                                 float down_scale_batch, float down_scale_channel, void* output) {
+    return act_silu((cudaStream_t)stream, input, input_scale_per_batch, input_scale_per_channel, optional_gate,
+                    gate_scale_per_batch, gate_scale_per_channel, batch, quant_dim, from_layout, 0.0f, down_scale_batch,
+                    down_scale_channel, nullptr, output, nullptr, false);
+}
+
+int32_t pplb200_i8i8_minmax_requantize_silu_fp16(pplb200_stream_t stream, const void* input, const void* input_scale_per_batch,
+                                                 const void* input_scale_per_channel, const void* optional_gate,
+                                                 const void* gate_scale_per_batch, const void* gate_scale_per_channel,
+                                                 int64_t batch, int64_t quant_dim, int32_t layout, float up_scale,
+                                                 float down_scale_batch, float down_scale_channel, void* workspace,
+                                                 void* output, void* scale) {
+    return act_silu((cudaStream_t)stream, input, input_scale_per_batch, input_scale_per_channel, optional_gate,
+                    gate_scale_per_batch, gate_scale_per_channel, batch, quant_dim, layout, up_scale, down_scale_batch,
+                    down_scale_channel, workspace, output, scale, true);
+}
+
+int32_t pplb200_i8i8_minmax_requantize_swiglu_fp16(pplb200_stream_t stream, const void* input, const void* input_scale_per_batch,
+                                                   const void* input_scale_per_channel, int64_t batch, int64_t quant_dim,
+                                                   float beta, int32_t layout, float up_scale, float down_scale_batch,
+                                                   float down_scale_channel, void* workspace, void* output, void* scale) {
+    return act_swiglu((cudaStream_t)stream, input, input_scale_per_batch, input_scale_per_channel, batch, quant_dim, beta, layout,
+                      up_scale, down_scale_batch, down_scale_channel, workspace, output, scale);
+}
+
 int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode) {
     (void)N; (void)K;
     return gemm_ws_bytes(M, epilogue_mode);

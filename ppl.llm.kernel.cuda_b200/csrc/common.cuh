@@ -80,6 +80,17 @@ int32_t launch_skip_rmsnorm_quantize(cudaStream_t stream, const half* input, con
                                      float eps, int64_t batch, int64_t dim, float up_scale, int32_t layout,
                                      half* skip_out, half* scale_out, int8_t* q);
 
+// consumers of the raw int32 accumulators (activation_requant.cu)
+int32_t act_silu(cudaStream_t stream, const void* input, const void* sb, const void* sc, const void* gate, const void* gsb,
+                 const void* gsc, int64_t batch, int64_t dim, int32_t layout, float up, float down_b, float down_c,
+                 void* workspace, void* out, void* scale_out, bool requant);
+int32_t act_swiglu(cudaStream_t stream, const void* input, const void* sb, const void* sc, int64_t batch, int64_t dim,
+                   float beta, int32_t layout, float up, float down_b, float down_c, void* workspace, void* out,
+                   void* scale_out);
+int32_t dequantize_split3(cudaStream_t stream, const void* acc, const void* bias, const void* sm, const void* sn,
+                          int64_t batch, int64_t dim, int64_t d0, int64_t d1, int64_t d2, float down_m, float down_n,
+                          int32_t layout, void* o0, void* o1, void* o2);
+
 int32_t launch_transpose01_f16(cudaStream_t stream, const half* in, int64_t d0, int64_t d1, int64_t d2, half* out);
 
 struct GemmArgs {

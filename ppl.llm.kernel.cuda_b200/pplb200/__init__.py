@@ -35,6 +35,8 @@ EXPORTS = [
     "pplb200_nccl_get_unique_id", "pplb200_nccl_comm_init", "pplb200_nccl_comm_destroy",
     "pplb200_i8i8_gemm_status", "pplb200_layout_offset",
     "pplb200_i8i8_gemm_requant_static_scratch", "pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16",
+    "pplb200_i8i8_minmax_dequantize_split3_fp16", "pplb200_i8i8_minmax_dequantize_silu_fp16",
+    "pplb200_i8i8_minmax_requantize_silu_fp16", "pplb200_i8i8_minmax_requantize_swiglu_fp16",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -50,6 +52,10 @@ def _load():
     lib.pplb200_last_error.restype = ctypes.c_char_p
     lib.pplb200_i8i8_minmax_quantize_fp16.argtypes = [vp, vp, i64, i64, f32, i32, vp, vp]
     lib.pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16.argtypes = [vp, vp, vp, vp, f32, i64, i64, f32, i32, vp, vp, vp]
+    lib.pplb200_i8i8_minmax_dequantize_split3_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, f32, i32, vp, vp, vp]
+    lib.pplb200_i8i8_minmax_dequantize_silu_fp16.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, f32, vp]
+    lib.pplb200_i8i8_minmax_requantize_silu_fp16.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, f32, f32, vp, vp, vp]
+    lib.pplb200_i8i8_minmax_requantize_swiglu_fp16.argtypes = [vp, vp, vp, vp, i64, i64, f32, i32, f32, f32, f32, vp, vp, vp]
     lib.pplb200_i8i8_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
     lib.pplb200_i8i8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.pplb200_i8i8_gemm_workspace_bytes.restype = i64
@@ -130,6 +136,51 @@ def skip_rmsnorm_minmax_quantize_fp16(x, weight, skip=None, eps=1e-5, up_scale=T
     _check(lib.pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16(_stream(), _ptr(x), _ptr(weight), _ptr(skip), eps, batch, dim,
                                                               up_scale, to_layout, _ptr(skip_out), _ptr(s), _ptr(q)))
     return skip_out, q, s
+
+
+def minmax_dequantize_split3_fp16(acc, scale_m, scale_n, splits, bias=None, down_m=TOKEN_DOWN_SCALE,
+                                  down_n=HIDDEN_DOWN_SCALE, from_layout=MATRIX_LAYOUT_ROW_MAJOR, shape=None):
+    import torch
+    batch, dim = shape if shape is not None else acc.shape
+    outs = [torch.empty((batch, d), dtype=torch.float16, device=acc.device) for d in splits]
+    _check(lib.pplb200_i8i8_minmax_dequantize_split3_fp16(_stream(), _ptr(acc), _ptr(bias), _ptr(scale_m), _ptr(scale_n), batch, dim,
+                                                          splits[0], splits[1], splits[2], down_m, down_n, from_layout,
+                                                          _ptr(outs[0]), _ptr(outs[1]), _ptr(outs[2])))
+    return outs
+
+
+def minmax_silu_fp16(acc, scale_m, scale_n, gate=None, gate_scale_m=None, gate_scale_n=None, requant=True,
+                     up_scale=TOKEN_UP_SCALE, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE,
+                     layout=MATRIX_LAYOUT_ROW_MAJOR):
+    """requant=True: (workspace fp16, q int8, scale fp16 [batch]); requant=False: fp16 output."""
+    import torch
+    batch, dim = acc.shape
+    if not requant:
+        out = torch.empty((batch, dim), dtype=torch.float16, device=acc.device)
+        _check(lib.pplb200_i8i8_minmax_dequantize_silu_fp16(_stream(), _ptr(acc), _ptr(scale_m), _ptr(scale_n), _ptr(gate),
+                                                            _ptr(gate_scale_m), _ptr(gate_scale_n), batch, dim, layout, down_m,
+                                                            down_n, _ptr(out)))
+        return out
+    ws = torch.empty((batch, dim), dtype=torch.float16, device=acc.device)
+    q = torch.empty((batch, dim), dtype=torch.int8, device=acc.device)
+    s = torch.empty((batch,), dtype=torch.float16, device=acc.device)
+    _check(lib.pplb200_i8i8_minmax_requantize_silu_fp16(_stream(), _ptr(acc), _ptr(scale_m), _ptr(scale_n), _ptr(gate),
+                                                        _ptr(gate_scale_m), _ptr(gate_scale_n), batch, dim, layout, up_scale,
+                                                        down_m, down_n, _ptr(ws), _ptr(q), _ptr(s)))
+    return ws, q, s
+
+
+def minmax_requantize_swiglu_fp16(acc, scale_m, scale_n, beta=1.0, up_scale=TOKEN_UP_SCALE, down_m=TOKEN_DOWN_SCALE,
+                                  down_n=HIDDEN_DOWN_SCALE, layout=MATRIX_LAYOUT_ROW_MAJOR):
+    """acc int32 [batch, 2 * dim] = [x | gate] -> (workspace fp16 [batch, dim], q int8, scale fp16 [batch])."""
+    import torch
+    batch, dim = acc.shape[0], acc.shape[1] // 2
+    ws = torch.empty((batch, dim), dtype=torch.float16, device=acc.device)
+    q = torch.empty((batch, dim), dtype=torch.int8, device=acc.device)
+    s = torch.empty((batch,), dtype=torch.float16, device=acc.device)
+    _check(lib.pplb200_i8i8_minmax_requantize_swiglu_fp16(_stream(), _ptr(acc), _ptr(scale_m), _ptr(scale_n), batch, dim, beta,
+                                                          layout, up_scale, down_m, down_n, _ptr(ws), _ptr(q), _ptr(s)))
+    return ws, q, s
 
 
 def minmax_dequantize_fp16(acc, scale_m, scale_n, bias=None, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE,

@@ -39,6 +39,8 @@ def _load():
     L.orc_gemm_i8i8i32_rows.restype = None
     L.orc_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
     L.orc_skip_rmsnorm_minmax_quantize_fp16.argtypes = [vp, vp, vp, f32, i64, i64, f32, i32, vp, vp, vp]
+    L.orc_activation_requantize.argtypes = [i32, vp, vp, vp, vp, vp, vp, i64, i64, f32, f32, f32, f32, vp, vp, vp]
+    L.orc_dequantize_split3.argtypes = [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, f32, vp, vp, vp]
     L.orc_w8a8_linear.argtypes = [vp, vp, vp, vp, i64, i64, i64, f32, f32, f32, f32, vp, vp, vp, vp, vp, vp]
     return L
 
@@ -131,6 +133,32 @@ def skip_rmsnorm_quantize(x, weight, skip=None, eps=1e-5, up_scale=TOKEN_UP, lay
     rc = L.orc_skip_rmsnorm_minmax_quantize_fp16(_p(x), _p(weight), _p(None if skip is None else _c(skip, np.float16)), eps,
                                                  M, K, up_scale, layout, _p(z), _p(s), _p(q))
     return rc, z, q, s
+
+
+def activation_requantize(kind, acc, scale_b, scale_c, gate=None, gate_scale_b=None, gate_scale_c=None, beta=1.0,
+                          up_scale=TOKEN_UP, down_b=TOKEN_DOWN, down_c=HIDDEN_DOWN):
+    """kind 0 SiLU, 1 gated SiLU, 2 SwiGLU (acc [M, 2 dim]).  Returns (workspace f16, q int8, scale f16)."""
+    acc = _c(acc, np.int32)
+    M = acc.shape[0]
+    dim = acc.shape[1] // 2 if kind == 2 else acc.shape[1]
+    ws = np.empty((M, dim), np.float16); q = np.empty((M, dim), np.int8); s = np.empty((M,), np.float16)
+    rc = L.orc_activation_requantize(kind, _p(acc), _p(_c(scale_b, np.float16)), _p(_c(scale_c, np.float16)),
+                                     _p(None if gate is None else _c(gate, np.int32)),
+                                     _p(None if gate_scale_b is None else _c(gate_scale_b, np.float16)),
+                                     _p(None if gate_scale_c is None else _c(gate_scale_c, np.float16)),
+                                     M, dim, beta, up_scale, down_b, down_c, _p(ws), _p(q), _p(s))
+    assert rc == 0
+    return ws, q, s
+
+
+def dequantize_split3(acc, scale_m, scale_n, splits, bias=None, down_m=TOKEN_DOWN, down_n=HIDDEN_DOWN):
+    acc = _c(acc, np.int32)
+    M, N = acc.shape
+    outs = [np.zeros((M, d), np.float16) for d in splits]
+    rc = L.orc_dequantize_split3(_p(acc), _p(None if bias is None else _c(bias, np.float16)), _p(_c(scale_m, np.float16)),
+                                 _p(_c(scale_n, np.float16)), M, N, splits[0], splits[1], splits[2], down_m, down_n,
+                                 _p(outs[0]), _p(outs[1]), _p(outs[2]))
+    return rc, outs
 
 
 def layout_offset(layout, rows, cols, r, c):

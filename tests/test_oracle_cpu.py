@@ -211,3 +211,25 @@ def test_skip_rmsnorm_quantize_vs_numpy(oracle):
     assert np.array_equal(q, qn)
     assert np.array_equal(bits(s), bits((scale * np.float32(4096)).astype(np.float16)))
     assert oracle.skip_rmsnorm_quantize(x, w, skip, layout=1)[0] == 2
+
+
+def test_activation_consumers_vs_numpy(oracle):
+    rng = np.random.default_rng(12)
+    M, D = 6, 96
+    acc = rng.integers(-(2 ** 20), 2 ** 20, (M, 2 * D), dtype=np.int32)
+    sm = (rng.uniform(0.5, 3.0, M) * 4096 / 127).astype(np.float16)
+    sn = (rng.uniform(0.5, 2.0, 2 * D) * 8192 / 2 ** 18).astype(np.float16)
+    ws, q, s = oracle.activation_requantize(2, acc, sm, sn, beta=1.0)
+    bs = (sm.astype(np.float32) * np.float32(1 / 4096))[:, None]
+    def dq(a, sc):
+        t = (a.astype(np.float32) * sc.astype(np.float32)[None, :]).astype(np.float32)
+        return ((t * np.float32(1 / 8192)).astype(np.float32) * bs).astype(np.float32)
+    x, g = dq(acc[:, :D], sn[:D]), dq(acc[:, D:], sn[D:])
+    res = ((x / (np.float32(1) + np.exp(-x).astype(np.float32))).astype(np.float32) * g).astype(np.float32)
+    assert np.abs(ws.astype(np.float32) - res).max() <= np.abs(res).max() * 2e-3
+    scale = np.maximum(np.abs(res).max(axis=1) / np.float32(127), np.float32(1e-7))
+    assert np.abs(s.astype(np.float32) - scale * 4096).max() <= (scale * 4096).max() * 2e-3
+    assert np.abs(q.astype(np.int32)).max() == 127
+    rc, outs = oracle.dequantize_split3(acc[:, :96].copy(), sm, sn[:96], (32, 48, 16))
+    rc2, full = oracle.dequantize(acc[:, :96].copy(), sm, sn[:96])
+    assert rc == 0 and np.array_equal(np.concatenate(outs, axis=1).view(np.uint16), full.view(np.uint16))
