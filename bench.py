@@ -534,6 +534,29 @@ def aux_kernels(steps, warmup):
         t = ms / steps * 1e-3
         out[name] = {"shape": [M, K], "us": t * 1e6, "gb_per_s": nbytes / t / 1e9,
                      "frac_of_measured_hbm": nbytes / t / 1e9 / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+    del xs, skip, q
+
+    # c2's real successor: the fused gate+up projection (GEMM + dequantize + SwiGLU + re-quantize in one
+    # pass) against the reference's structure (raw int32 linear, then the stand-alone SwiGLU kernel).
+    M, K, D = 4096, 4096, 11008
+    xq = torch.randint(-127, 128, (M, K), generator=g, device="cuda", dtype=torch.int8)
+    ws_ = [torch.randint(-127, 128, (2 * D, K), generator=g, device="cuda", dtype=torch.int8) for _ in range(2)]
+    sm = (torch.rand(M, device="cuda") + 0.5).half()
+    sn = (torch.rand(2 * D, device="cuda") * 1e-2 + 1e-3).half()
+    scratch = torch.empty((pplb200.lib.pplb200_i8i8_gate_up_swiglu_workspace_bytes(M, D, K),), dtype=torch.uint8, device="cuda")
+    outs = (torch.empty((M, D), dtype=torch.float16, device="cuda"), torch.empty((M, D), dtype=torch.int8, device="cuda"),
+            torch.empty((M,), dtype=torch.float16, device="cuda"))
+    acc = torch.empty((M, 2 * D), dtype=torch.int32, device="cuda")
+
+    def two_step(i):
+        pplb200.column_parallel_linear(xq, ws_[i % 2], None, None, None, K, 2 * D, gather_output=False, out=acc)
+        pplb200.minmax_requantize_swiglu_fp16(acc, sm, sn)
+
+    for name, fn in (("gate_up_swiglu_requant (fused)", lambda i: pplb200.gate_up_swiglu_requant(xq, ws_[i % 2], sm, sn, ws=scratch, out=outs)),
+                     ("raw linear + minmax_requantize_swiglu_fp16", two_step)):
+        ms = _time_steps(_Eager(fn), steps, warmup, 1)
+        t = ms / steps * 1e-3
+        out[name] = {"shape": [M, K, 2 * D], "us": t * 1e6, "tops": 2.0 * M * 2 * D * K / t / 1e12}
     return out
 
 

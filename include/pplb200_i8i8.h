@@ -111,6 +111,25 @@ int32_t pplb200_i8i8_minmax_requantize_swiglu_fp16(pplb200_stream_t stream, cons
                                                    float down_scale_channel, void* workspace, void* output, void* scale);
 
 /*
+ * Fused gate+up projection: GEMM + dequantize + SwiGLU + per-token re-quantize in one pass over the
+ * accumulators (they never leave tensor memory as int32).  Same result, bit for bit, as
+ * column_parallel_linear(gather_output = false) followed by minmax_requantize_swiglu_fp16
+ *   (src/.../pmx/i8i8/column_parallel_linear.cu:81-85,136; src/.../pmx/i8i8/swiglu.cu:42-185),
+ * which is how the reference runs this layer (two kernels and a 4 * M * 2 * act_dim byte round trip).
+ * input int8 [M, K] (row stride lda); weight int8 [2 * act_dim, K] = [x rows | gate rows];
+ * scale_N fp16 [2 * act_dim]; activated fp16 [M, act_dim] (the reference's `workspace`);
+ * out_q int8 [M, act_dim]; out_q_scale fp16 [M].  ws: pplb200_i8i8_gate_up_swiglu_workspace_bytes().
+ * Shapes that cannot use the fused kernel (M <= 128, act_dim % 128 != 0, too few tiles) run the two
+ * steps separately inside this call (the workspace size accounts for the int32 buffer).
+ */
+int64_t pplb200_i8i8_gate_up_swiglu_workspace_bytes(int64_t M, int64_t act_dim, int64_t K);
+int32_t pplb200_i8i8_gate_up_swiglu_requant(pplb200_stream_t stream, const void* input, int64_t lda, const void* weight,
+                                            int64_t M, int64_t act_dim, int64_t K, const void* scale_M,
+                                            const void* scale_N, float beta, float up_scale, float down_scale_M,
+                                            float down_scale_N, void* ws, int64_t ws_bytes, void* activated,
+                                            void* out_q, void* out_q_scale);
+
+/*
  * Scratch bytes pplb200_i8i8_gemm needs for (M, N, K, mode).  0 means `ws` may be NULL.
  */
 int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode);

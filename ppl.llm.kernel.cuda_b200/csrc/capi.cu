@@ -193,6 +193,61 @@ int32_t pplb200_i8i8_minmax_requantize_swiglu_fp16(pplb200_stream_t stream, cons
                       up_scale, down_scale_batch, down_scale_channel, workspace, output, scale);
 }
 
+namespace {
+// The fused form needs the CTA-pair kernel: enough 256-row x 128-channel tiles for every pair, and
+// the x / gate halves of the weight matrix aligned to the 128-row tiles.
+bool swiglu_fusable(int64_t M, int64_t D) { return M > 128 && D % 128 == 0 && ((M + 255) / 256) * (D / 128) >= 74; }
+}
+
+int64_t pplb200_i8i8_gate_up_swiglu_workspace_bytes(int64_t M, int64_t act_dim, int64_t K) {
+    (void)K;
+    const int64_t maxima = round_up(M * 4 + 4, WS_ALIGN);
+    return swiglu_fusable(M, act_dim) ? maxima : maxima + round_up(M * 2 * act_dim * 4, WS_ALIGN);
+}
+
+int32_t pplb200_i8i8_gate_up_swiglu_requant(pplb200_stream_t stream_, const void* input, int64_t lda, const void* weight,
+                                            int64_t M, int64_t act_dim, int64_t K, const void* scale_M,
+                                            const void* scale_N, float beta, float up_scale, float down_scale_M,
+                                            float down_scale_N, void* ws, int64_t ws_bytes, void* activated,
+                                            void* out_q, void* out_q_scale) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const int64_t D = act_dim;
+    if (M < 0 || D < 0 || K <= 0) return fail(RC_INVALID_VALUE, "bad extents");
+    if (M == 0 || D == 0) return RC_SUCCESS;
+    if (K % 16 || lda % 16 || lda < K || D % 16) return fail(RC_INVALID_VALUE, "K, lda, act_dim must be multiples of 16 and lda >= K");
+    if (!input || !weight || !scale_M || !scale_N || !activated || !out_q || !out_q_scale) return fail(RC_INVALID_VALUE, "null pointer");
+    if (!aligned16(input) || !aligned16(weight) || !aligned16(scale_N) || !aligned16(activated) || !aligned16(out_q))
+        return fail(RC_INVALID_VALUE, "operands must be 16-byte aligned");
+    const int64_t need = pplb200_i8i8_gate_up_swiglu_workspace_bytes(M, D, K);
+    if (!ws || ws_bytes < need) return fail(RC_INVALID_VALUE, "workspace too small: %lld < %lld", (long long)ws_bytes, (long long)need);
+    if ((reinterpret_cast<uintptr_t>(ws) & (WS_ALIGN - 1)) != 0) return fail(RC_INVALID_VALUE, "workspace must be 256-byte aligned");
+    uint32_t* maxima = (uint32_t*)ws;
+
+    if (!swiglu_fusable(M, D)) {
+        // small problems: raw int32 GEMM, then the stand-alone SwiGLU + re-quantize kernel
+        void* acc = (char*)ws + round_up(M * 4 + 4, WS_ALIGN);
+        int32_t rc = gemm_entry(stream, input, lda, weight, K, M, 2 * D, K, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f,
+                                nullptr, 0, acc, 2 * D, nullptr, nullptr, false);
+        if (rc != RC_SUCCESS) return rc;
+        return act_swiglu(stream, acc, scale_M, scale_N, M, D, beta, LAYOUT_ROW_MAJOR, up_scale, down_scale_M, down_scale_N,
+                          activated, out_q, out_q_scale);
+    }
+
+    if (cudaMemsetAsync(maxima, 0, (size_t)M * 4, stream) != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
+    GemmArgs g;
+    g.A = (const int8_t*)input; g.lda = lda; g.B = (const int8_t*)weight; g.ldb = K;
+    g.M = M; g.N = 2 * D; g.K = K; g.mode = EPI_SWIGLU_F16;
+    g.scale_m = (const half*)scale_M; g.scale_n = (const half*)scale_N; g.bias = nullptr;
+    g.down_m = down_scale_M; g.down_n = down_scale_N;
+    g.out = activated; g.ldc = D;
+    g.row_absmax_bits = maxima;
+    g.beta = beta;
+    int32_t rc = launch_gemm(stream, g);
+    if (rc != RC_SUCCESS) return rc;
+    return launch_quantize(stream, (const half*)activated, M, D, up_scale, LAYOUT_ROW_MAJOR, (int8_t*)out_q, (half*)out_q_scale,
+                           maxima, nullptr, false);
+}
+
 int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode) {
     (void)N; (void)K;
     return gemm_ws_bytes(M, epilogue_mode);

@@ -30,6 +30,7 @@ enum : int32_t {
     EPI_RAW_I32 = 0,
     EPI_DEQUANT_F16 = 1,
     EPI_DEQUANT_F16_REQUANT_I8 = 2,
+    EPI_SWIGLU_F16 = 3, // internal: fused gate+up projection, see pplb200_i8i8_gate_up_swiglu_requant
 };
 
 // Records a message retrievable through pplb200_last_error() and returns `rc`.
@@ -103,6 +104,7 @@ struct GemmArgs {
     void* out; int64_t ldc;
     uint32_t* row_absmax_bits; // mode 2: per-row max |y| as float bits, zeroed by the launcher
     bool pdl = false;          // launch as a programmatic dependent of the preceding kernel
+    float beta = 1.0f;         // EPI_SWIGLU_F16
 };
 int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int* status, bool pdl);
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);

@@ -45,6 +45,9 @@ struct KernelParams {
     float down_m, down_n;
     uint32_t* row_absmax_bits;
     unsigned int* status;
+    // EPI_SWIGLU_F16 (CTA-pair kernel only): B = [x rows | gate rows], act_dim rows each
+    int32_t act_dim;
+    float beta;
 };
 
 template <int BN> struct Cfg {
@@ -263,7 +266,10 @@ struct PairCfg {
     static constexpr int TMEM_COLS = 512;                   // two accumulator buffers of 256 columns
 };
 
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+// EW = number of epilogue warps (4, or 8 for the transcendental-heavy SwiGLU epilogue, where two
+// warps share a TMEM lane quarter and split the columns).
+template <int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                             const KernelParams p) {
     using C = PairCfg;
@@ -289,7 +295,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(ptx::smem_addr(&acc_full_bar[b]), 1);
-            ptx::mbar_init(ptx::smem_addr(&acc_empty_bar[b]), 2 * EPI_WARPS); // the epilogue warps of both CTAs
+            ptx::mbar_init(ptx::smem_addr(&acc_empty_bar[b]), 2 * EW); // the epilogue warps of both CTAs
         }
         ptx::fence_mbar_init();
     }
@@ -316,7 +322,10 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                 const int m_tile = tile % p.num_m_tiles;
                 const int n_tile = tile / p.num_m_tiles;
                 const int row_a = m_tile * 256 + (int)rank * BM;
-                const int row_b = n_tile * C::BN + (int)rank * C::HALF_N;
+                // SwiGLU: the leader stages 128 "x" weight rows, its partner the 128 "gate" rows of the same
+                // output channels, so accumulator columns [0,128) and [128,256) pair up element by element
+                const int row_b = p.mode == EPI_SWIGLU_F16 ? n_tile * C::HALF_N + (int)rank * p.act_dim
+                                                           : n_tile * C::BN + (int)rank * C::HALF_N;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&empty_bar[stage]), phase ^ 1u, p.status, ST_PRODUCER_TIMEOUT)) {
                         ok = false;
@@ -372,7 +381,9 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     } else {
         // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
         const int quarter = warp & 3;
-        const int col_begin = ((warp - 2) >> 2) * (C::BN / (EPI_WARPS / 4)), col_end = col_begin + C::BN / (EPI_WARPS / 4);
+        constexpr int COL_GROUPS = EW / 4;
+        const int col_group = (warp - 2) >> 2;
+        const int col_begin = col_group * (C::BN / COL_GROUPS), col_end = col_begin + C::BN / COL_GROUPS;
         const bool has_bias = p.bias != nullptr;
         int it = 0;
         for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
@@ -388,6 +399,47 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             if (p.mode != EPI_RAW_I32 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
             __half absmax = __float2half_rn(0.0f);
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::BN;
+
+            if (p.mode == EPI_SWIGLU_F16) {
+                // out[m, n] = fp16( silu_beta(dq(x)) * dq(gate) ), operation order of the reference's
+                // stand-alone kernel (swiglu.cu:92-99); row maximum of the fp32 value before rounding
+                float fmax_row = 0.0f;
+#pragma unroll 1
+                for (int c0 = col_group * (C::HALF_N / COL_GROUPS); c0 < (col_group + 1) * (C::HALF_N / COL_GROUPS); c0 += 32) {
+                    const int n0 = n_tile * C::HALF_N + c0;
+                    if (n0 >= p.N) break; // warp-uniform; p.N == act_dim here
+                    uint32_t ax[32], ag[32];
+                    ptx::tmem_ld_32x32(taddr_row + c0, ax);
+                    ptx::tmem_ld_32x32(taddr_row + C::HALF_N + c0, ag);
+                    ptx::tmem_ld_wait();
+                    if (!row_ok) continue;
+                    half* dst = reinterpret_cast<half*>(p.out) + (int64_t)row * p.ldc + n0;
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        if (n0 + j >= p.N) break;
+                        const uint4 sxv = *reinterpret_cast<const uint4*>(p.scale_n + n0 + j);
+                        const uint4 sgv = *reinterpret_cast<const uint4*>(p.scale_n + p.act_dim + n0 + j);
+                        const half* sx = reinterpret_cast<const half*>(&sxv);
+                        const half* sg = reinterpret_cast<const half*>(&sgv);
+                        uint4 ov;
+                        half* o = reinterpret_cast<half*>(&ov);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float x = __fmul_rn(__fmul_rn(__fmul_rn((float)(int32_t)ax[j + e], __half2float(sx[e])), p.down_n), batch_scale);
+                            const float g = __fmul_rn(__fmul_rn(__fmul_rn((float)(int32_t)ag[j + e], __half2float(sg[e])), p.down_n), batch_scale);
+                            const float r = __fmul_rn(__fdiv_rn(x, __fadd_rn(1.0f, __expf(__fmul_rn(-x, p.beta)))), g);
+                            o[e] = __float2half_rn(r);
+                            fmax_row = fmaxf(fabsf(r), fmax_row);
+                        }
+                        *reinterpret_cast<uint4*>(dst + j) = ov;
+                    }
+                }
+                if (row_ok) atomicMax(p.row_absmax_bits + row, __float_as_uint(fmax_row));
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
+                continue;
+            }
 
 #pragma unroll 1
             for (int c0 = col_begin; c0 < col_end; c0 += 32) {
@@ -489,7 +541,9 @@ const DeviceInfo* device_info() {
         if (cudaGetSymbolAddress(&addr, g_gemm_status) != cudaSuccess) return nullptr;
         d.status = static_cast<unsigned int*>(addr);
         if (!set_smem_attr<256>() || !set_smem_attr<128>() || !set_smem_attr<64>() || !set_smem_attr<32>()) return nullptr;
-        if (cudaFuncSetAttribute(gemm_i8_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_i8_tcgen05_pair_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 PairCfg::SMEM_BYTES) != cudaSuccess) return nullptr;
+        if (cudaFuncSetAttribute(gemm_i8_tcgen05_pair_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  PairCfg::SMEM_BYTES) != cudaSuccess) return nullptr;
         d.ready = true;
     }
@@ -534,12 +588,19 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     p.down_m = a.down_m; p.down_n = a.down_n;
     p.row_absmax_bits = a.row_absmax_bits;
     p.status = dev.status;
+    p.act_dim = 0; p.beta = a.beta;
+    if (a.mode == EPI_SWIGLU_F16) { // a.N = 2 * act_dim weight rows; the output has act_dim columns
+        p.act_dim = (int32_t)(a.N / 2);
+        p.N = p.act_dim;
+        p.num_n_tiles = (int32_t)((p.act_dim + PairCfg::HALF_N - 1) / PairCfg::HALF_N);
+    }
     const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
     int64_t pairs = dev.sms / 2;
     if (tiles < pairs) pairs = tiles;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
-    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    const bool wide_epilogue = a.mode == EPI_SWIGLU_F16;
+    cfg.blockDim = dim3(wide_epilogue ? 64 + 32 * 8 : 64 + 32 * 4, 1, 1);
     cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
     cfg.stream = stream;
     cudaLaunchAttribute attr;
@@ -549,7 +610,8 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel, ta, tb, p);
+    const cudaError_t e = wide_epilogue ? cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<8>, ta, tb, p)
+                                        : cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<4>, ta, tb, p);
     if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "pair GEMM launch failed: %s", cudaGetErrorString(e));
     return RC_SUCCESS;
 }
@@ -562,6 +624,8 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     if (!dev) return fail(RC_DEVICE_RUNTIME_ERROR, "device set-up failed: %s", cudaGetErrorString(cudaGetLastError()));
     if (a.M > INT32_MAX - BM || a.N > INT32_MAX - 256 || a.K > INT32_MAX - BK)
         return fail(RC_UNSUPPORTED, "GEMM extent beyond 2^31");
+
+    if (a.mode == EPI_SWIGLU_F16) return launch_pair(stream, a, *dev); // the caller checked the shape
 
     // Up to 128 tokens the op is bound by the weight stream: dedicated small-batch kernel.
     if (a.M <= 128) return launch_gemm_decode(stream, a, dev->status, a.pdl);

@@ -37,6 +37,7 @@ EXPORTS = [
     "pplb200_i8i8_gemm_requant_static_scratch", "pplb200_i8i8_skip_rmsnorm_minmax_quantize_fp16",
     "pplb200_i8i8_minmax_dequantize_split3_fp16", "pplb200_i8i8_minmax_dequantize_silu_fp16",
     "pplb200_i8i8_minmax_requantize_silu_fp16", "pplb200_i8i8_minmax_requantize_swiglu_fp16",
+    "pplb200_i8i8_gate_up_swiglu_workspace_bytes", "pplb200_i8i8_gate_up_swiglu_requant",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -56,6 +57,9 @@ def _load():
     lib.pplb200_i8i8_minmax_dequantize_silu_fp16.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, f32, vp]
     lib.pplb200_i8i8_minmax_requantize_silu_fp16.argtypes = [vp, vp, vp, vp, vp, vp, vp, i64, i64, i32, f32, f32, f32, vp, vp, vp]
     lib.pplb200_i8i8_minmax_requantize_swiglu_fp16.argtypes = [vp, vp, vp, vp, i64, i64, f32, i32, f32, f32, f32, vp, vp, vp]
+    lib.pplb200_i8i8_gate_up_swiglu_workspace_bytes.argtypes = [i64, i64, i64]
+    lib.pplb200_i8i8_gate_up_swiglu_workspace_bytes.restype = i64
+    lib.pplb200_i8i8_gate_up_swiglu_requant.argtypes = [vp, vp, i64, vp, i64, i64, i64, vp, vp, f32, f32, f32, f32, vp, i64, vp, vp, vp]
     lib.pplb200_i8i8_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
     lib.pplb200_i8i8_gemm_workspace_bytes.argtypes = [i64, i64, i64, i32]
     lib.pplb200_i8i8_gemm_workspace_bytes.restype = i64
@@ -181,6 +185,23 @@ def minmax_requantize_swiglu_fp16(acc, scale_m, scale_n, beta=1.0, up_scale=TOKE
     _check(lib.pplb200_i8i8_minmax_requantize_swiglu_fp16(_stream(), _ptr(acc), _ptr(scale_m), _ptr(scale_n), batch, dim, beta,
                                                           layout, up_scale, down_m, down_n, _ptr(ws), _ptr(q), _ptr(s)))
     return ws, q, s
+
+
+def gate_up_swiglu_requant(xq, w, scale_m, scale_n, beta=1.0, up_scale=TOKEN_UP_SCALE, down_m=TOKEN_DOWN_SCALE,
+                           down_n=HIDDEN_DOWN_SCALE, ws=None, out=None):
+    """xq int8 [M,K], w int8 [2D,K] = [x | gate] rows -> (activated fp16 [M,D], q int8 [M,D], scale fp16 [M])."""
+    import torch
+    M, K = xq.shape
+    D = w.shape[0] // 2
+    need = lib.pplb200_i8i8_gate_up_swiglu_workspace_bytes(M, D, K)
+    if ws is None:
+        ws = torch.empty((need,), dtype=torch.uint8, device=xq.device)
+    act, q, s = out if out is not None else (torch.empty((M, D), dtype=torch.float16, device=xq.device),
+                                            torch.empty((M, D), dtype=torch.int8, device=xq.device),
+                                            torch.empty((M,), dtype=torch.float16, device=xq.device))
+    _check(lib.pplb200_i8i8_gate_up_swiglu_requant(_stream(), _ptr(xq), xq.stride(0), _ptr(w), M, D, K, _ptr(scale_m), _ptr(scale_n),
+                                                   beta, up_scale, down_m, down_n, _ptr(ws), ws.numel(), _ptr(act), _ptr(q), _ptr(s)))
+    return act, q, s
 
 
 def minmax_dequantize_fp16(acc, scale_m, scale_n, bias=None, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE,

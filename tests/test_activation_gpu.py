@@ -152,3 +152,22 @@ def test_activation_error_codes(cuda):
     with pytest.raises(pplb200.PplError) as e:
         pplb200.minmax_dequantize_split3_fp16(acc, s4, s64, (30, 30, 4))
     assert e.value.rc == pplb200.RC_INVALID_VALUE
+
+
+@pytest.mark.parametrize("M,D,K", [(2304, 1152, 272), (4096, 1280, 512), (64, 256, 128), (300, 208, 144)])  # fused (first two) and fallback
+def test_fused_gate_up_swiglu_matches_two_step(cuda, oracle, M, D, K):
+    """GEMM + SwiGLU + re-quantize in one pass == raw-int32 linear followed by the stand-alone SwiGLU kernel, bit for bit."""
+    import pplb200
+    rng = np.random.default_rng(M + D + K)
+    xq = _t(cuda, rng.integers(-127, 128, (M, K), dtype=np.int8))
+    w = _t(cuda, rng.integers(-127, 128, (2 * D, K), dtype=np.int8))
+    sm = _t(cuda, (rng.uniform(0.5, 3.0, M) * 4096 / 127).astype(np.float16))
+    sn = _t(cuda, (rng.uniform(0.5, 2.0, 2 * D) * 8192 * 127 / (1.5 * 5400 * np.sqrt(K))).astype(np.float16))
+    acc = pplb200.column_parallel_linear(xq, w, None, None, None, K, 2 * D, gather_output=False)
+    ws2, q2, s2 = pplb200.minmax_requantize_swiglu_fp16(acc, sm, sn, beta=1.3)
+    act, q, s = pplb200.gate_up_swiglu_requant(xq, w, sm, sn, beta=1.3)
+    cuda.cuda.synchronize()
+    assert pplb200.gemm_status() == 0
+    assert cuda.equal(act.view(cuda.int16), ws2.view(cuda.int16))
+    assert cuda.equal(s.view(cuda.int16), s2.view(cuda.int16)) and cuda.equal(q, q2)
+    assert float(act.float().abs().max()) > 0.01  # the scales put the values in SiLU's interesting range
