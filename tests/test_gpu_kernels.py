@@ -170,6 +170,33 @@ def test_gemm_raw_i32(cuda, oracle, M, N, K):
         assert np.array_equal(c[r].cpu().numpy(), oracle.gemm_rows(a, b, r, r + 1)[0])
 
 
+DECODE_SHAPES = [(128, 6272, 2048), (100, 12288, 4096), (64, 8192, 1024), (72, 3200, 512), (128, 12288, 1024), (40, 4096, 4096)]
+
+
+@pytest.mark.parametrize("M,N,K", DECODE_SHAPES)
+def test_decode_gemm_all_modes(cuda, oracle, M, N, K):
+    """Small-batch kernel across its variants: one or two weight-row tiles per CTA, K split over clusters of
+    different sizes, an odd number of weight-row tiles, token counts that are not multiples of 8."""
+    import pplb200
+    rng = np.random.default_rng(M + N + K)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    sn = (rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float16)
+    ref = oracle.linear(x, w, sn, bias, requant=True)
+    txq, tw, tsm, tsn, tb = _t(cuda, ref["xq"]), _t(cuda, w), _t(cuda, ref["sm"]), _t(cuda, sn), _t(cuda, bias)
+    acc = pplb200.gemm_i8i8(txq, tw)
+    y = pplb200.gemm_i8i8(txq, tw, mode=pplb200.EPI_DEQUANT_F16, scale_m=tsm, scale_n=tsn, bias=tb)
+    y2, yq, ys = pplb200.gemm_i8i8(txq, tw, mode=pplb200.EPI_DEQUANT_F16_REQUANT_I8, scale_m=tsm, scale_n=tsn, bias=tb)
+    cuda.cuda.synchronize()
+    assert pplb200.gemm_status() == 0
+    assert np.array_equal(acc.cpu().numpy(), ref["acc"])
+    assert np.array_equal(oracle.f16_bits(y.cpu().numpy()), oracle.f16_bits(ref["y"]))
+    assert np.array_equal(oracle.f16_bits(y2.cpu().numpy()), oracle.f16_bits(ref["y"]))
+    assert np.array_equal(yq.cpu().numpy(), ref["yq"])
+    assert np.array_equal(oracle.f16_bits(ys.cpu().numpy()), oracle.f16_bits(ref["ys"]))
+
+
 def test_gemm_extreme_values(cuda):
     """All-(-128) x all-(-128): the largest products; also +127 x -128 (the reference's own test data includes -128)."""
     import pplb200
