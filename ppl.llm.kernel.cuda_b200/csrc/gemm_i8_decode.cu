@@ -36,13 +36,6 @@ constexpr int SMEM_BUDGET = 210 * 1024; // one CTA per SM: the whole shared memo
 
 constexpr unsigned ST_DEC_PRODUCER = 16u, ST_DEC_MMA = 32u, ST_DEC_EPI = 64u;
 
-#ifdef PPLB200_TIMING
-__device__ unsigned long long g_dbg_times[8 * 1024];
-#define PPLB200_STAMP(slot) do { if (threadIdx.x == 64) { unsigned long long gt; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(gt)); g_dbg_times[(blockIdx.y * gridDim.x + blockIdx.x) * 8 + (slot)] = gt; } } while (0)
-#else
-#define PPLB200_STAMP(slot) do { } while (0)
-#endif
-
 struct DecodeParams {
     int32_t M, N;           // tokens, weight rows
     int32_t num_k_blocks;
@@ -177,7 +170,6 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    PPLB200_STAMP(4);
     const uint32_t ring = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t S = cluster_nctarank();
     const uint32_t rank = cluster_ctarank();
@@ -213,7 +205,6 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    PPLB200_STAMP(0);
 
     // per-thread output column (= weight row) and its constants; these belong to the weights, not to
     // the preceding kernel, so they are fetched now and their latency hides behind the main loop
@@ -282,7 +273,6 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     const bool acc_ready = nkb == 0 || ptx::mbar_wait(ptx::smem_addr(&acc_full_bar), 0, p.status, ST_DEC_EPI);
     ptx::tc_fence_after();
     pdl_launch_dependents();
-    PPLB200_STAMP(1);
 
     const uint32_t taddr_row = tmem_base + ((uint32_t)(q * 32) << 16);
     const uint32_t recv_pieces_per_owner = (C::PIECES + S - 1) / S;
@@ -321,15 +311,11 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
             }
         }
         cluster_sync_all(); // all partial pieces have landed
-        PPLB200_STAMP(2);
     } else {
         __syncthreads(); // token_scale visible
     }
 
     // ---- epilogue over the pieces this CTA owns
-#ifdef PPLB200_EXP_NOSTORE
-    uint32_t dbg_acc = 0;
-#endif
     const int mode = p.mode;
     const int M = p.M;
     const float down_n = p.down_n;
@@ -385,11 +371,7 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                         half* dst = reinterpret_cast<half*>(p.out) + (int64_t)m0 * p.ldc + n;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-#ifdef PPLB200_EXP_NOSTORE
-                            dbg_acc ^= (uint32_t)__half_as_ushort(h[j]) + (uint32_t)(m0 + j);
-#else
                             if (n_ok && m0 + j < M) dst[(int64_t)j * p.ldc] = h[j];
-#endif
                         if (mode == EPI_DEQUANT_F16_REQUANT_I8) {
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
@@ -411,10 +393,6 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     }
 
 #undef PPLB200_KB
-#ifdef PPLB200_EXP_NOSTORE
-    if (dbg_acc == 0x12345u) reinterpret_cast<uint32_t*>(p.out)[threadIdx.x] = dbg_acc;
-#endif
-    PPLB200_STAMP(3);
     ptx::tc_fence_before();
     __syncthreads();
     if (p.mode == EPI_DEQUANT_F16_REQUANT_I8) {
@@ -539,11 +517,5 @@ int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int*
     if (a.M <= 64) return launch_bt<64>(stream, a, *dev, status, pdl);
     return launch_bt<128>(stream, a, *dev, status, pdl);
 }
-
-#ifdef PPLB200_TIMING
-extern "C" __attribute__((visibility("default"))) int pplb200_debug_times(unsigned long long* host, int n) {
-    return (int)cudaMemcpyFromSymbol(host, g_dbg_times, sizeof(unsigned long long) * n);
-}
-#endif
 
 } // namespace pplb200

@@ -21,7 +21,7 @@ def declared_symbols():
 def test_library_exports_every_declared_symbol():
     import pplb200
     names = declared_symbols()
-    assert len(names) >= 14
+    assert len(names) >= 22
     for n in names:
         assert hasattr(pplb200.lib, n), "missing export: " + n
     assert set(names) == set(pplb200.EXPORTS)
@@ -80,8 +80,25 @@ ppl::common::RetCode run(cudaStream_t s, cublasLtHandle_t lt, k::cublas::AlgoCac
     rc = k::cublas::gemm_i8i8i32(s, lt, nullptr, false, 4096, ppl::common::DATATYPE_INT8, xq, true, 4096,
         ppl::common::DATATYPE_INT8, w, nullptr, 16, 4096, 4096, 1, 0, 0, ws, cache, 4096, ppl::common::DATATYPE_INT32, qbuf);
     if (rc != ppl::common::RC_SUCCESS) return rc;
-    return k::pmx::i8i8::minmax_dequantize_fp16(s, qbuf, bias, sm, sn, 16, 4096, k::pmx::i8i8::token_down_scale,
+    rc = k::pmx::i8i8::minmax_dequantize_fp16(s, qbuf, bias, sm, sn, 16, 4096, k::pmx::i8i8::token_down_scale,
         k::pmx::i8i8::hidden_down_scale, k::MATRIX_LAYOUT_ROW_MAJOR, y);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    // the producers / consumers around the linear, same argument lists as the reference header
+    rc = k::pmx::i8i8::skip_rmsnorm_minmax_quantize_fp16(s, x, w, nullptr, 1e-5f, 16, 4096, k::pmx::i8i8::token_up_scale,
+        k::MATRIX_LAYOUT_ROW_MAJOR, y, sm, xq);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    rc = k::pmx::i8i8::minmax_dequantize_split3_fp16(s, qbuf, bias, sm, sn, 16, 4096, 2048, 1024, 1024,
+        k::pmx::i8i8::token_down_scale, k::pmx::i8i8::hidden_down_scale, k::MATRIX_LAYOUT_ROW_MAJOR, y, y, y);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    rc = k::pmx::i8i8::minmax_requantize_silu_fp16(s, qbuf, sm, sn, nullptr, nullptr, nullptr, 16, 4096,
+        k::MATRIX_LAYOUT_ROW_MAJOR, k::pmx::i8i8::token_up_scale, k::pmx::i8i8::token_down_scale,
+        k::pmx::i8i8::hidden_down_scale, y, xq, sm);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    rc = k::pmx::i8i8::minmax_dequantize_silu_fp16(s, qbuf, sm, sn, nullptr, nullptr, nullptr, 16, 4096,
+        k::MATRIX_LAYOUT_ROW_MAJOR, k::pmx::i8i8::token_down_scale, k::pmx::i8i8::hidden_down_scale, y);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    return k::pmx::i8i8::minmax_requantize_swiglu_fp16(s, qbuf, sm, sn, 16, 2048, 1.0f, k::MATRIX_LAYOUT_ROW_MAJOR,
+        k::pmx::i8i8::token_up_scale, k::pmx::i8i8::token_down_scale, k::pmx::i8i8::hidden_down_scale, y, xq, sm);
 }
 int main() {
     k::MatrixLayoutHelper<k::MATRIX_LAYOUT_COL32> h;
