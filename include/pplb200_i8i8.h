@@ -233,6 +233,51 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream, const void* in
                                          void* ws, int64_t ws_bytes, void* output);
 
 /*
+ * Row-parallel linear over peer-mapped memory (ranks of one NVLink domain, one GPU per rank,
+ * size <= 8).  Same result as pplb200_i8i8_row_parallel_linear with reduce_mode 0 -- bit-identical
+ * to the unsharded linear -- but without a collective library on the data path: the GEMM stores
+ * each raw int32 tile into the buffer of the rank that owns those output rows while it computes
+ * the next tiles, the owner sums the `size` partials, applies scale and bias once, and the other
+ * ranks fetch its finished fp16 rows.  Stands where the reference runs dequantize + fp16
+ * all-reduce (src/ppl/kernel/llm/cuda/pmx/i8i8/row_parallel_linear.cu:113-160).
+ *
+ * Set-up, once per process and rank (these calls allocate and synchronise; the linear does not):
+ *   pplb200_p2p_create        cudaMalloc of `bytes` (>= pplb200_i8i8_row_parallel_p2p_bytes of the
+ *                             largest M, N used) on the current device, flags cleared.
+ *   pplb200_p2p_export        64-byte inter-process handle of that buffer (host memory).
+ *   pplb200_p2p_connect       maps the peers' buffers from the handles of all ranks (size x 64
+ *                             bytes, rank order, exchanged by the caller); every rank must have
+ *                             created its context before any rank's first linear call.
+ *   pplb200_p2p_connect_local same, for contexts created in this process (one process driving
+ *                             several devices): `peer_ctx` holds `size` context pointers.
+ *
+ * The linear: all ranks call it with the same M, N, K, in the same order on their contexts.
+ * M % size == 0 (else RC_UNSUPPORTED: use the collective path), out_features % 8 == 0,
+ * (in_features / size) % 16 == 0.  `input` is this rank's K shard [M, in_features / size] with
+ * leading dimension input_ld (0: dense); scale_M are the full-row scales [M]; weight is the
+ * shard [out_features, in_features / size]; output fp16 [M, out_features] is complete on every
+ * rank when the call's work on `stream` has finished.
+ * `phases`: 7 for the whole operation.  The bits (1 produce, 2 reduce, 4 gather) let one process
+ * that drives several ranks on one stream enqueue the phases rank after rank.
+ * Waits on peers are bounded (about two seconds); pplb200_p2p_status returns a non-zero word
+ * when one expired (bit 0: partial sums missing, bit 1: finished rows missing) -- the output of
+ * that call is then undefined and later calls do not wait until the word is reset.
+ */
+int64_t pplb200_i8i8_row_parallel_p2p_bytes(int64_t M, int64_t out_features, int32_t size);
+int32_t pplb200_p2p_create(int32_t rank, int32_t size, int64_t bytes, void** ctx_out);
+int32_t pplb200_p2p_export(void* ctx, void* handle64_host);
+int32_t pplb200_p2p_connect(void* ctx, const void* handles_host);
+int32_t pplb200_p2p_connect_local(void* ctx, void* const* peer_ctx);
+int32_t pplb200_p2p_destroy(void* ctx);
+int32_t pplb200_p2p_status(void* ctx, int32_t reset);
+int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream, void* ctx, const void* input, int64_t M,
+                                             int64_t input_ld, const void* weight, const void* optional_bias,
+                                             const void* scale_M, const void* scale_N,
+                                             float down_scale_M, float down_scale_N,
+                                             int64_t in_features, int64_t out_features,
+                                             int32_t phases, void* output);
+
+/*
  * NCCL plumbing for callers that do not already own a communicator (tests, bench).
  * unique id: 128 bytes, host memory.  Not part of the reference surface (ppl.nn.llm creates
  * its communicators itself and hands them over in ppl::common::NcclParam).

@@ -31,7 +31,10 @@ enum : int32_t {
     EPI_DEQUANT_F16 = 1,
     EPI_DEQUANT_F16_REQUANT_I8 = 2,
     EPI_SWIGLU_F16 = 3, // internal: fused gate+up projection, see pplb200_i8i8_gate_up_swiglu_requant
+    EPI_PUSH_I32 = 4,   // internal: raw int32 tiles stored into the row owner's peer-mapped buffer
 };
+
+constexpr int kMaxPeers = 8;
 
 // Records a message retrievable through pplb200_last_error() and returns `rc`.
 int32_t fail(int32_t rc, const char* fmt, ...);
@@ -105,6 +108,10 @@ struct GemmArgs {
     uint32_t* row_absmax_bits; // mode 2: per-row max |y| as float bits, zeroed by the launcher
     bool pdl = false;          // launch as a programmatic dependent of the preceding kernel
     float beta = 1.0f;         // EPI_SWIGLU_F16
+    // EPI_PUSH_I32: output row r belongs to rank r / push_rows; it is stored at
+    // push_base[owner] + ((push_rank * push_rows + r % push_rows) * ldc + col) (int32 elements).
+    int32_t* push_base[kMaxPeers] = {};
+    int32_t push_rows = 0, push_rank = 0;
 };
 int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int* status, bool pdl);
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);

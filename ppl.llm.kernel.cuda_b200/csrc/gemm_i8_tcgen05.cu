@@ -48,6 +48,9 @@ struct KernelParams {
     // EPI_SWIGLU_F16 (CTA-pair kernel only): B = [x rows | gate rows], act_dim rows each
     int32_t act_dim;
     float beta;
+    // EPI_PUSH_I32 (CTA-pair kernel only): see GemmArgs
+    int32_t* push_base[kMaxPeers];
+    int32_t push_rows, push_rank;
 };
 
 template <int BN> struct Cfg {
@@ -279,6 +282,9 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     __shared__ __align__(8) uint64_t acc_full_bar[2];       // per CTA: accumulator buffer complete
     __shared__ __align__(8) uint64_t acc_empty_bar[2];      // used in the leader: both CTAs drained the buffer
     __shared__ uint32_t tmem_base_slot;
+    // EPI_PUSH_I32: one 32 x 32 int32 block per epilogue warp, to turn "one row per lane" into
+    // 128-byte contiguous row segments before the stores leave for another GPU
+    __shared__ __align__(16) uint4 push_stage[EW == 4 ? 4 : 1][256];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -396,7 +402,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             const int row = m_tile * 256 + (int)rank * BM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
             float batch_scale = 0.0f;
-            if (p.mode != EPI_RAW_I32 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
+            if (p.mode != EPI_RAW_I32 && p.mode != EPI_PUSH_I32 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
             __half absmax = __float2half_rn(0.0f);
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::BN;
 
@@ -435,6 +441,49 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                     }
                 }
                 if (row_ok) atomicMax(p.row_absmax_bits + row, __float_as_uint(fmax_row));
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
+                continue;
+            }
+
+            if (EW == 4 && p.mode == EPI_PUSH_I32) {
+                // Raw int32 tile, each row stored into the buffer of the rank that owns it.  Lane l holds
+                // row l of the warp's 32 x 32 block; after the exchange through shared memory lane l
+                // stores 16 bytes of row 4 i + l / 8 (i = 0..7), so a warp-wide store covers four
+                // complete 128-byte lines.
+                uint4* tr = push_stage[EW == 4 ? warp - 2 : 0];
+                const int sub = lane >> 3, chunk = lane & 7;
+                int32_t* dst_row[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int r = m_tile * 256 + (int)rank * BM + quarter * 32 + 4 * i + sub;
+                    dst_row[i] = nullptr;
+                    if (r < p.M) {
+                        const int owner = r / p.push_rows;
+                        dst_row[i] = p.push_base[owner] + ((int64_t)p.push_rank * p.push_rows + (r - owner * p.push_rows)) * p.ldc;
+                    }
+                }
+#pragma unroll 1
+                for (int c0 = 0; c0 < C::BN; c0 += 32) {
+                    const int n0 = n_tile * C::BN + c0;
+                    if (n0 >= p.N) break; // warp-uniform
+                    uint32_t acc[32];
+                    ptx::tmem_ld_32x32(taddr_row + c0, acc);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        tr[lane * 8 + (j ^ (lane & 7))] = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+                    __syncwarp();
+                    const int col = n0 + chunk * 4;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = 4 * i + sub;
+                        const uint4 v = tr[r * 8 + (chunk ^ (r & 7))];
+                        if (dst_row[i] != nullptr && col < p.N) *reinterpret_cast<uint4*>(dst_row[i] + col) = v;
+                    }
+                    __syncwarp();
+                }
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
@@ -555,7 +604,7 @@ int32_t launch_bn(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev)
     CUtensorMap ta, tb;
     if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
     if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, BN)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
-    KernelParams p;
+    KernelParams p{};
     p.M = (int32_t)a.M; p.N = (int32_t)a.N;
     p.num_m_tiles = (int32_t)((a.M + BM - 1) / BM);
     p.num_n_tiles = (int32_t)((a.N + BN - 1) / BN);
@@ -577,7 +626,7 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     CUtensorMap ta, tb;
     if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
     if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, PairCfg::HALF_N)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
-    KernelParams p;
+    KernelParams p{};
     p.M = (int32_t)a.M; p.N = (int32_t)a.N;
     p.num_m_tiles = (int32_t)((a.M + 255) / 256);
     p.num_n_tiles = (int32_t)((a.N + PairCfg::BN - 1) / PairCfg::BN);
@@ -589,6 +638,8 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     p.row_absmax_bits = a.row_absmax_bits;
     p.status = dev.status;
     p.act_dim = 0; p.beta = a.beta;
+    for (int i = 0; i < kMaxPeers; ++i) p.push_base[i] = a.push_base[i];
+    p.push_rows = a.push_rows; p.push_rank = a.push_rank;
     if (a.mode == EPI_SWIGLU_F16) { // a.N = 2 * act_dim weight rows; the output has act_dim columns
         p.act_dim = (int32_t)(a.N / 2);
         p.N = p.act_dim;
@@ -625,7 +676,7 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     if (a.M > INT32_MAX - BM || a.N > INT32_MAX - 256 || a.K > INT32_MAX - BK)
         return fail(RC_UNSUPPORTED, "GEMM extent beyond 2^31");
 
-    if (a.mode == EPI_SWIGLU_F16) return launch_pair(stream, a, *dev); // the caller checked the shape
+    if (a.mode == EPI_SWIGLU_F16 || a.mode == EPI_PUSH_I32) return launch_pair(stream, a, *dev); // the caller checked the shape
 
     // Up to 128 tokens the op is bound by the weight stream: dedicated small-batch kernel.
     if (a.M <= 128) return launch_gemm_decode(stream, a, dev->status, a.pdl);

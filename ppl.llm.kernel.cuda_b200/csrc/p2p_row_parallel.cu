@@ -1,0 +1,357 @@
+// Row-parallel i8i8 linear whose reduction runs over peer-mapped GPU memory instead of a
+// collective library: the GEMM's epilogue stores every raw int32 tile straight into the buffer of
+// the rank that owns those output rows (so the transfer over NVLink runs under the main loop of the
+// following tiles), the owner sums the partials exactly, applies the dequant epilogue once, and the
+// other ranks fetch the finished fp16 rows.
+//
+//   rank r, rows [r * Ms, (r + 1) * Ms), Ms = M / size
+//   buffer of every rank:  | flags 4 KiB | recv int32 [size][Ms][N] | staging fp16 [Ms][N] |
+//
+//   produce : GEMM (K shard) -> tile rows of owner o go to  peer[o].recv[r]           (remote stores)
+//             signal(0)      -> peer[*].flags[0][r] = epoch                           (release, system scope)
+//   reduce  : wait(0)        -> flags[0][*] >= epoch                                  (acquire, bounded)
+//             recv[0] + .. + recv[size-1] -> dequant + bias -> output rows, staging
+//             signal(1)
+//   gather  : wait(1); output rows of every other rank <- peer[s].staging            (remote loads)
+//
+// Same arithmetic as the unsharded fused linear (integer sums, then the three rounded products),
+// hence bit-identical to it.  Replaces, for ranks of one NVLink domain, the dequantize + fp16
+// all-reduce of the reference (src/ppl/kernel/llm/cuda/pmx/i8i8/row_parallel_linear.cu:28-162).
+//
+// Buffer reuse needs no extra barrier: a rank's next produce follows its gather, which follows
+// every peer's signal(1), which follows that peer's reduce (the last reader of its recv buffer);
+// and a rank's next reduce (the next writer of its staging) follows every peer's next signal(0),
+// which follows that peer's gather (the last reader of this rank's staging).
+//
+// Every wait is bounded; on expiry a code is ORed into the context's status word, later waits
+// of that context return at once, and the result is undefined until the status is cleared.
+#include "common.cuh"
+#include "../../include/pplb200_i8i8.h"
+
+#include <new>
+#include <string.h>
+
+namespace pplb200 {
+namespace {
+
+constexpr int64_t kFlagBytes = 4096;
+constexpr int kStatusWord = 64;         // uint32 index inside the flag page
+constexpr long long kPeerWaitCycles = 4000000000LL;
+constexpr unsigned ST_WAIT_PARTIALS = 1u, ST_WAIT_ROWS = 2u;
+
+struct Ctx {
+    int32_t rank = 0, size = 1, device = 0;
+    uint8_t* base = nullptr;
+    int64_t bytes = 0;
+    uint8_t* peer[kMaxPeers] = {};
+    bool opened[kMaxPeers] = {};
+    bool connected = false;
+    uint32_t epoch = 0;
+};
+
+struct Peers {
+    uint8_t* base[kMaxPeers];
+    int32_t rank, size;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// system-scope load that is not served from this SM's L1: the line lives in another GPU's memory
+__device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// flags[phase][src] of every peer <- epoch.  Launched after the kernel whose stores it publishes.
+__global__ void p2p_signal_kernel(Peers pr, int phase, uint32_t epoch) {
+    const int t = threadIdx.x;
+    if (t < pr.size) {
+        __threadfence_system();
+        st_release_sys(reinterpret_cast<uint32_t*>(pr.base[t]) + phase * kMaxPeers + pr.rank, epoch);
+    }
+}
+
+// Block-wide: returns when every rank's flag of `phase` has reached `epoch`, or when the cycle
+// budget is spent (status |= code), or at once when the status word is already set.
+__device__ __forceinline__ void wait_flags(uint32_t* flag_page, int phase, int size, uint32_t epoch, unsigned code) {
+    if ((int)threadIdx.x < size) {
+        uint32_t* status = flag_page + kStatusWord;
+        const uint32_t* f = flag_page + phase * kMaxPeers + threadIdx.x;
+        if (*reinterpret_cast<volatile uint32_t*>(status) == 0) {
+            const long long t0 = clock64();
+            for (uint32_t spin = 1; (int32_t)(ld_acquire_sys(f) - epoch) < 0; ++spin) {
+                if ((spin & 0xffu) == 0) {
+                    if (clock64() - t0 > kPeerWaitCycles) { atomicOr(status, code); break; }
+                    if (*reinterpret_cast<volatile uint32_t*>(status) != 0) break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+}
+
+// Sums the `size` partial slices of this rank's rows and applies the dequant epilogue:
+// 8 columns per item.  Writes the rows into the caller's output and into the staging copy.
+__global__ void __launch_bounds__(256)
+p2p_reduce_dequant_kernel(uint32_t* flag_page, int size, uint32_t epoch, const int32_t* __restrict__ recv,
+                          int64_t rows, int64_t dim, const half* __restrict__ scale_m, const half* __restrict__ scale_n,
+                          const half* __restrict__ bias, float down_m, float down_n, half* __restrict__ out_rows,
+                          half* __restrict__ staging) {
+    wait_flags(flag_page, 0, size, epoch, ST_WAIT_PARTIALS);
+    const int64_t chunks_per_row = dim >> 3;
+    const int64_t total = rows * chunks_per_row;
+    const int64_t slice = rows * dim;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t m = i / chunks_per_row;
+        const int64_t n = (i - m * chunks_per_row) << 3;
+        const int32_t* src = recv + m * dim + n;
+        int4 a0 = *reinterpret_cast<const int4*>(src);
+        int4 a1 = *reinterpret_cast<const int4*>(src + 4);
+        for (int s = 1; s < size; ++s) {
+            const int4 b0 = *reinterpret_cast<const int4*>(src + s * slice);
+            const int4 b1 = *reinterpret_cast<const int4*>(src + s * slice + 4);
+            a0.x += b0.x; a0.y += b0.y; a0.z += b0.z; a0.w += b0.w;
+            a1.x += b1.x; a1.y += b1.y; a1.z += b1.z; a1.w += b1.w;
+        }
+        const float bs = __fmul_rn(__half2float(scale_m[m]), down_m);
+        const uint4 snv = *reinterpret_cast<const uint4*>(scale_n + n);
+        const half* sn = reinterpret_cast<const half*>(&snv);
+        const int32_t a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        uint4 ov;
+        half* o = reinterpret_cast<half*>(&ov);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            // three separately rounded products in the order of the fused GEMM epilogue
+            float t = __fmul_rn((float)a[j], __half2float(sn[j]));
+            t = __fmul_rn(t, down_n);
+            t = __fmul_rn(t, bs);
+            o[j] = __float2half_rn(t);
+        }
+        if (bias != nullptr) {
+            const uint4 bv = *reinterpret_cast<const uint4*>(bias + n);
+            const half* b = reinterpret_cast<const half*>(&bv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = __hadd(o[j], b[j]);
+        }
+        *reinterpret_cast<uint4*>(out_rows + m * dim + n) = ov;
+        *reinterpret_cast<uint4*>(staging + m * dim + n) = ov;
+    }
+}
+
+// Copies the finished fp16 rows of every other rank from its staging area into this rank's output.
+// Work is cut into 4 KiB pieces (256 threads x 16 bytes); consecutive pieces read different peers,
+// starting with rank + 1, so all links carry traffic at once and no two ranks start on the same peer.
+__global__ void __launch_bounds__(256)
+p2p_gather_kernel(Peers pr, uint32_t epoch, int64_t staging_offset, int64_t rows, int64_t dim, half* __restrict__ out) {
+    wait_flags(reinterpret_cast<uint32_t*>(pr.base[pr.rank]), 1, pr.size, epoch, ST_WAIT_ROWS);
+    const int others = pr.size - 1;
+    const int64_t vec_per_slice = rows * dim >> 3;
+    const int64_t pieces = ((vec_per_slice + 255) >> 8) * others;
+    for (int64_t piece = blockIdx.x; piece < pieces; piece += gridDim.x) {
+        const int q = (int)(piece % others);
+        const int64_t v = (piece / others) * 256 + threadIdx.x;
+        if (v >= vec_per_slice) continue;
+        int src = pr.rank + 1 + q;
+        if (src >= pr.size) src -= pr.size;
+        const uint4* from = reinterpret_cast<const uint4*>(pr.base[src] + staging_offset) + v;
+        reinterpret_cast<uint4*>(out + (int64_t)src * rows * dim)[v] = ld_peer_v4(from);
+    }
+}
+
+int64_t recv_bytes(int64_t M, int64_t N) { return round_up(M * N * 4, 256); }
+int64_t staging_bytes(int64_t M, int64_t N, int32_t size) { return round_up(M / size * N * 2, 256); }
+
+Peers peers_of(const Ctx& c) {
+    Peers p;
+    for (int i = 0; i < kMaxPeers; ++i) p.base[i] = c.peer[i];
+    p.rank = c.rank; p.size = c.size;
+    return p;
+}
+
+} // namespace
+} // namespace pplb200
+
+using namespace pplb200;
+
+extern "C" {
+
+int64_t pplb200_i8i8_row_parallel_p2p_bytes(int64_t M, int64_t N, int32_t size) {
+    if (M < 0 || N < 0 || size < 1 || size > kMaxPeers) return -1;
+    return kFlagBytes + recv_bytes(M, N) + staging_bytes(M, N, size);
+}
+
+int32_t pplb200_p2p_create(int32_t rank, int32_t size, int64_t bytes, void** ctx_out) {
+    clear_error();
+    if (!ctx_out) return fail(RC_INVALID_VALUE, "ctx_out is null");
+    if (size < 1 || size > kMaxPeers || rank < 0 || rank >= size) return fail(RC_INVALID_VALUE, "bad rank/size %d/%d", rank, size);
+    if (bytes < kFlagBytes) return fail(RC_INVALID_VALUE, "buffer smaller than the flag page");
+    Ctx* c = new (std::nothrow) Ctx;
+    if (!c) return fail(RC_DEVICE_RUNTIME_ERROR, "out of host memory");
+    c->rank = rank; c->size = size; c->bytes = bytes;
+    if (cudaGetDevice(&c->device) != cudaSuccess || cudaMalloc((void**)&c->base, (size_t)bytes) != cudaSuccess) {
+        const int32_t rc = fail(RC_DEVICE_RUNTIME_ERROR, "cudaMalloc of %lld bytes failed: %s", (long long)bytes, cudaGetErrorString(cudaGetLastError()));
+        delete c;
+        return rc;
+    }
+    if (cudaMemset(c->base, 0, (size_t)kFlagBytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        cudaFree(c->base);
+        delete c;
+        return fail(RC_DEVICE_RUNTIME_ERROR, "clearing the flag page failed");
+    }
+    c->peer[rank] = c->base;
+    c->connected = size == 1;
+    *ctx_out = c;
+    return RC_SUCCESS;
+}
+
+int32_t pplb200_p2p_export(void* ctx, void* handle64_host) {
+    clear_error();
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    Ctx* c = (Ctx*)ctx;
+    if (!c || !handle64_host) return fail(RC_INVALID_VALUE, "null argument");
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, c->base) != cudaSuccess)
+        return fail(RC_DEVICE_RUNTIME_ERROR, "cudaIpcGetMemHandle failed: %s", cudaGetErrorString(cudaGetLastError()));
+    memcpy(handle64_host, &h, 64);
+    return RC_SUCCESS;
+}
+
+int32_t pplb200_p2p_connect(void* ctx, const void* handles_host) {
+    clear_error();
+    Ctx* c = (Ctx*)ctx;
+    if (!c || !handles_host) return fail(RC_INVALID_VALUE, "null argument");
+    for (int r = 0; r < c->size; ++r) {
+        if (r == c->rank || c->peer[r] != nullptr) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles_host + 64 * r, 64);
+        void* p = nullptr;
+        if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess)
+            return fail(RC_DEVICE_RUNTIME_ERROR, "cudaIpcOpenMemHandle(rank %d) failed: %s", r, cudaGetErrorString(cudaGetLastError()));
+        c->peer[r] = (uint8_t*)p;
+        c->opened[r] = true;
+    }
+    c->connected = true;
+    return RC_SUCCESS;
+}
+
+int32_t pplb200_p2p_connect_local(void* ctx, void* const* peer_ctx) {
+    clear_error();
+    Ctx* c = (Ctx*)ctx;
+    if (!c || !peer_ctx) return fail(RC_INVALID_VALUE, "null argument");
+    for (int r = 0; r < c->size; ++r) {
+        if (r == c->rank) continue;
+        const Ctx* o = (const Ctx*)peer_ctx[r];
+        if (!o || o->rank != r || o->size != c->size || o->bytes != c->bytes)
+            return fail(RC_INVALID_VALUE, "peer context %d does not match", r);
+        if (o->device != c->device) {
+            int can = 0;
+            if (cudaDeviceCanAccessPeer(&can, c->device, o->device) != cudaSuccess || !can)
+                return fail(RC_UNSUPPORTED, "device %d cannot access device %d", c->device, o->device);
+            const cudaError_t e = cudaDeviceEnablePeerAccess(o->device, 0);
+            if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled)
+                return fail(RC_DEVICE_RUNTIME_ERROR, "cudaDeviceEnablePeerAccess failed: %s", cudaGetErrorString(e));
+            cudaGetLastError();
+        }
+        c->peer[r] = o->base;
+    }
+    c->connected = true;
+    return RC_SUCCESS;
+}
+
+int32_t pplb200_p2p_destroy(void* ctx) {
+    Ctx* c = (Ctx*)ctx;
+    if (!c) return RC_SUCCESS;
+    cudaDeviceSynchronize();
+    for (int r = 0; r < c->size; ++r)
+        if (c->opened[r]) cudaIpcCloseMemHandle(c->peer[r]);
+    cudaFree(c->base);
+    delete c;
+    return RC_SUCCESS;
+}
+
+int32_t pplb200_p2p_status(void* ctx, int32_t reset) {
+    Ctx* c = (Ctx*)ctx;
+    if (!c) return -1;
+    uint32_t v = 0;
+    uint32_t* word = reinterpret_cast<uint32_t*>(c->base) + kStatusWord;
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    if (cudaMemcpy(&v, word, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (reset && v != 0) {
+        const uint32_t z = 0;
+        cudaMemcpy(word, &z, 4, cudaMemcpyHostToDevice);
+    }
+    return (int32_t)v;
+}
+
+int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx, const void* input, int64_t M,
+                                             int64_t input_ld, const void* weight, const void* optional_bias,
+                                             const void* scale_M, const void* scale_N, float down_scale_M,
+                                             float down_scale_N, int64_t in_features, int64_t out_features,
+                                             int32_t phases, void* output) {
+    clear_error();
+    cudaStream_t stream = (cudaStream_t)stream_;
+    Ctx* c = (Ctx*)ctx;
+    if (!c) return fail(RC_INVALID_VALUE, "null context");
+    if (!c->connected) return fail(RC_INVALID_VALUE, "context is not connected to its peers");
+    if (phases < 1 || phases > 7) return fail(RC_INVALID_VALUE, "phases must be a mask of 1 (produce), 2 (reduce), 4 (gather)");
+    const int32_t size = c->size, rank = c->rank;
+    if (M < 0 || in_features <= 0 || out_features < 0) return fail(RC_INVALID_VALUE, "negative extent");
+    if (in_features % size) return fail(RC_INVALID_VALUE, "in_features %% size != 0");
+    if (M % size) return fail(RC_UNSUPPORTED, "M %% size != 0: use the collective-library path");
+    const int64_t N = out_features, Kw = in_features / size, Ms = M / size;
+    const int64_t lda = input_ld > 0 ? input_ld : Kw;
+    if (N % 8 || Kw % 16) return fail(RC_UNSUPPORTED, "needs out_features %% 8 == 0 and (in_features / size) %% 16 == 0");
+    if (M > INT32_MAX / 2 || N > INT32_MAX / 2) return fail(RC_UNSUPPORTED, "extent beyond 2^30");
+    if (!input || !weight || !scale_M || !scale_N || !output) return fail(RC_INVALID_VALUE, "null pointer argument");
+    if (!aligned16(input) || !aligned16(weight) || !aligned16(output) || !aligned16(scale_N) || lda % 16 ||
+        (optional_bias && !aligned16(optional_bias)))
+        return fail(RC_INVALID_VALUE, "operands must be 16-byte aligned (pointers and leading dimension)");
+    if (pplb200_i8i8_row_parallel_p2p_bytes(M, N, size) > c->bytes)
+        return fail(RC_INVALID_VALUE, "peer buffer too small for M=%lld N=%lld", (long long)M, (long long)N);
+    if (M == 0 || N == 0) return RC_SUCCESS;
+
+    const int64_t recv_off = kFlagBytes, staging_off = kFlagBytes + recv_bytes(M, N);
+    const Peers pr = peers_of(*c);
+    uint32_t* flag_page = reinterpret_cast<uint32_t*>(c->base);
+
+    if (phases & 1) {
+        c->epoch += 1;
+        GemmArgs g;
+        g.A = (const int8_t*)input; g.lda = lda; g.B = (const int8_t*)weight; g.ldb = Kw;
+        g.M = M; g.N = N; g.K = Kw; g.mode = EPI_PUSH_I32;
+        g.scale_m = nullptr; g.scale_n = nullptr; g.bias = nullptr;
+        g.down_m = 0.f; g.down_n = 0.f;
+        g.out = nullptr; g.ldc = N;
+        g.row_absmax_bits = nullptr;
+        for (int r = 0; r < size; ++r) g.push_base[r] = reinterpret_cast<int32_t*>(c->peer[r] + recv_off);
+        g.push_rows = (int32_t)Ms; g.push_rank = rank;
+        const int32_t rc = launch_gemm(stream, g);
+        if (rc != RC_SUCCESS) return rc;
+        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, 0, c->epoch);
+    }
+    if (phases & 2) {
+        int64_t blocks = (Ms * (N >> 3) + 255) / 256;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        p2p_reduce_dequant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
+            flag_page, size, c->epoch, reinterpret_cast<const int32_t*>(c->base + recv_off), Ms, N,
+            (const half*)scale_M + (int64_t)rank * Ms, (const half*)scale_N, (const half*)optional_bias, down_scale_M,
+            down_scale_N, (half*)output + (int64_t)rank * Ms * N, reinterpret_cast<half*>(c->base + staging_off));
+        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, 1, c->epoch);
+    }
+    if ((phases & 4) && size > 1) {
+        int64_t blocks = ((Ms * N >> 3) + 255) / 256 * (size - 1);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        p2p_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(pr, c->epoch, staging_off, Ms, N, (half*)output);
+    }
+    return check_launch("row_parallel_linear_p2p");
+}
+
+}

@@ -38,6 +38,8 @@ EXPORTS = [
     "pplb200_i8i8_minmax_dequantize_split3_fp16", "pplb200_i8i8_minmax_dequantize_silu_fp16",
     "pplb200_i8i8_minmax_requantize_silu_fp16", "pplb200_i8i8_minmax_requantize_swiglu_fp16",
     "pplb200_i8i8_gate_up_swiglu_workspace_bytes", "pplb200_i8i8_gate_up_swiglu_requant",
+    "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
+    "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -75,6 +77,15 @@ def _load():
                                                         i32, i32, vp, i32, vp, vp, vp, i64, vp]
     lib.pplb200_i8i8_row_parallel_linear.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
                                                      i32, i32, vp, i32, i32, vp, vp, i64, vp]
+    lib.pplb200_i8i8_row_parallel_p2p_bytes.argtypes = [i64, i64, i32]
+    lib.pplb200_i8i8_row_parallel_p2p_bytes.restype = i64
+    lib.pplb200_p2p_create.argtypes = [i32, i32, i64, ctypes.POINTER(vp)]
+    lib.pplb200_p2p_export.argtypes = [vp, vp]
+    lib.pplb200_p2p_connect.argtypes = [vp, vp]
+    lib.pplb200_p2p_connect_local.argtypes = [vp, ctypes.POINTER(vp)]
+    lib.pplb200_p2p_destroy.argtypes = [vp]
+    lib.pplb200_p2p_status.argtypes = [vp, i32]
+    lib.pplb200_i8i8_row_parallel_linear_p2p.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32, vp]
     lib.pplb200_nccl_get_unique_id.argtypes = [vp]
     lib.pplb200_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
     lib.pplb200_nccl_comm_destroy.argtypes = [vp]
@@ -342,3 +353,51 @@ def nccl_comm_init(uid, rank, size):
 
 def nccl_comm_destroy(comm):
     _check(lib.pplb200_nccl_comm_destroy(comm))
+
+
+class P2PContext:
+    """One rank's peer-mapped buffer for `row_parallel_linear_p2p` (cudaMalloc'd by the library on
+    the current device).  Ranks in different processes exchange `handle()` bytes themselves and call
+    `connect(all_handles)`; ranks driven by one process use `connect_local(contexts)`."""
+
+    def __init__(self, rank, size, max_m, max_n):
+        self.rank, self.size = rank, size
+        self.bytes = lib.pplb200_i8i8_row_parallel_p2p_bytes(max_m, max_n, size)
+        if self.bytes < 0:
+            raise ValueError("bad extents for a peer buffer")
+        self.ctx = ctypes.c_void_p()
+        _check(lib.pplb200_p2p_create(rank, size, self.bytes, ctypes.byref(self.ctx)))
+
+    def handle(self):
+        buf = ctypes.create_string_buffer(64)
+        _check(lib.pplb200_p2p_export(self.ctx, buf))
+        return bytes(buf.raw)
+
+    def connect(self, handles):
+        assert len(handles) == self.size and all(len(h) == 64 for h in handles)
+        blob = b"".join(handles)  # length given explicitly: create_string_buffer(bytes) would add a terminator
+        _check(lib.pplb200_p2p_connect(self.ctx, ctypes.create_string_buffer(blob, len(blob))))
+
+    def connect_local(self, contexts):
+        arr = (ctypes.c_void_p * self.size)(*[c.ctx for c in contexts])
+        _check(lib.pplb200_p2p_connect_local(self.ctx, arr))
+
+    def status(self, reset=True):
+        return lib.pplb200_p2p_status(self.ctx, 1 if reset else 0)
+
+    def destroy(self):
+        if self.ctx:
+            lib.pplb200_p2p_destroy(self.ctx)
+            self.ctx = ctypes.c_void_p()
+
+
+def row_parallel_linear_p2p(p2p, xq, w, scale_m, scale_n, bias, in_features, out_features, out=None, phases=7,
+                            down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE):
+    import torch
+    M = xq.shape[0]
+    if out is None:
+        out = torch.empty((M, out_features), dtype=torch.float16, device=xq.device)
+    _check(lib.pplb200_i8i8_row_parallel_linear_p2p(_stream(), p2p.ctx, _ptr(xq), M, xq.stride(0), _ptr(w), _ptr(bias),
+                                                    _ptr(scale_m), _ptr(scale_n), down_m, down_n, in_features,
+                                                    out_features, phases, _ptr(out)))
+    return out

@@ -28,3 +28,9 @@ def cuda():
     import pplb200  # raises if the shared library is missing: no fallback
     torch.cuda.set_device(0)
     return torch
+
+
+@pytest.fixture(scope="session")
+def pplb200(cuda):
+    import pplb200 as lib
+    return lib
