@@ -278,7 +278,8 @@ def build_ours(wk):
         return step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes
 
     # row parallel: quantize the full activation rows (full-K absmax), GEMM on this rank's K shard,
-    # exact int32 all-reduce, dequant epilogue.
+    # exact int32 reduction, dequant epilogue.  Default: the reduction over peer-mapped memory (GEMM
+    # epilogue pushes tiles to the row owner); --row-reduce nccl selects reduce-scatter / all-gather.
     import torch.distributed as dist
     uid = [pplb200.nccl_unique_id() if wk.rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
@@ -286,14 +287,47 @@ def build_ours(wk):
     wk.comm = comm
     xq_full = torch.empty((M, K), dtype=torch.int8, device=dev)
     sm = torch.empty((M,), dtype=torch.float16, device=dev)
-    qbuf = torch.empty((M, N), dtype=torch.int32, device=dev)
     y = torch.empty((M, N), dtype=torch.float16, device=dev)
+    wk.row_reduce = "nccl"
+    qbuf = None
+    if wk.row_reduce_wanted == "p2p" and M % wk.world == 0:
+        ok, p2p = 1, None
+        try:
+            p2p = pplb200.P2PContext(wk.rank, wk.world, M, N)
+            mine = p2p.handle()
+        except pplb200.PplError as e:
+            ok, mine = 0, b"\0" * 64
+            sys.stderr.write("rank %d: peer buffer not available (%s)\n" % (wk.rank, e))
+        handles = [None] * wk.world
+        dist.all_gather_object(handles, (ok, mine))
+        if all(h[0] for h in handles):
+            try:
+                p2p.connect([h[1] for h in handles])
+            except pplb200.PplError as e:
+                ok = 0
+                sys.stderr.write("rank %d: mapping the peers' buffers failed (%s)\n" % (wk.rank, e))
+        else:
+            ok = 0
+        oks = [None] * wk.world
+        dist.all_gather_object(oks, ok)
+        if all(oks):
+            wk.row_reduce, wk.p2p = "p2p", p2p
+        elif p2p is not None:
+            p2p.destroy()
+    if wk.row_reduce == "nccl":
+        qbuf = torch.empty((M, N), dtype=torch.int32, device=dev)
+
+    def linear(s):
+        if wk.row_reduce == "p2p":
+            pplb200.row_parallel_linear_p2p(wk.p2p, xq_full[:, wk.k0:wk.k1], wk.w[s], sm, wk.sn, wk.bias, K, N, out=y)
+        else:
+            pplb200.row_parallel_linear(xq_full[:, wk.k0:wk.k1], wk.w[s], sm, wk.sn, wk.bias, K, N, rank=wk.rank,
+                                        size=wk.world, comm=comm, quant_buffer=qbuf, out=y)
 
     def step(i):
         s = i % wk.nsets
         pplb200.minmax_quantize_fp16(wk.x[s], out=xq_full, scale=sm)
-        pplb200.row_parallel_linear(xq_full[:, wk.k0:wk.k1], wk.w[s], sm, wk.sn, wk.bias, K, N, rank=wk.rank,
-                                    size=wk.world, comm=comm, quant_buffer=qbuf, out=y)
+        linear(s)
 
     x_stage = torch.empty_like(wk.x[0])
     y_host = torch.empty((M, N), dtype=torch.float16).pin_memory()
@@ -302,16 +336,18 @@ def build_ours(wk):
         s = i % wk.nsets
         x_stage.copy_(wk.x_host, non_blocking=True)
         pplb200.minmax_quantize_fp16(x_stage, out=xq_full, scale=sm)
-        pplb200.row_parallel_linear(xq_full[:, wk.k0:wk.k1], wk.w[s], sm, wk.sn, wk.bias, K, N, rank=wk.rank,
-                                    size=wk.world, comm=comm, quant_buffer=qbuf, out=y)
+        linear(s)
         y_host.copy_(y, non_blocking=True)
+
+    raw = torch.empty((M, N), dtype=torch.int32, device=dev) if qbuf is None else qbuf
 
     def kernel_only(i):
         s = i % wk.nsets
-        pplb200.gemm_i8i8(xq_full[:, wk.k0:wk.k1], wk.w[s], out=qbuf)
+        pplb200.gemm_i8i8(xq_full[:, wk.k0:wk.k1], wk.w[s], out=raw)
 
     gemm_bytes = M * Kw + N * Kw + 4 * M * N
-    return step, e2e, kernel_only, 3, wk.x_host.numel() * 2, M * N * 2, gemm_bytes
+    launches = 6 if wk.row_reduce == "p2p" else 3  # quantizer, GEMM, 2 flag kernels, reduce + dequant, row fetch
+    return step, e2e, kernel_only, launches, wk.x_host.numel() * 2, M * N * 2, gemm_bytes
 
 
 class RefLib:
@@ -418,6 +454,7 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
     from pplb200 import workloads as wl
     peaks = _peaks()
     wk = Workload(name, rank, world, sharded)
+    wk.row_reduce_wanted = args.row_reduce
     if impl == "ours":
         step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes = build_ours(wk)
     else:
@@ -503,6 +540,17 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
                                 "frac_of_4500_datasheet": ach / 4500.0}
     if want_cpu and rank == 0 and impl == "ours":
         line["cpu_baseline"] = cpu_baseline(name)
+    if getattr(wk, "row_reduce", None) is not None:
+        line["config"]["row_reduce"] = ("int32 tiles pushed to the row owner over peer-mapped memory, fp16 rows fetched back"
+                                        if wk.row_reduce == "p2p" else "NCCL int32 reduce-scatter + fp16 all-gather")
+    if getattr(wk, "p2p", None) is not None:
+        st = wk.p2p.status()
+        torch.cuda.synchronize()
+        import torch.distributed as dist
+        dist.barrier()  # no rank unmaps its buffer while a peer may still read it
+        wk.p2p.destroy()
+        if st != 0:
+            raise RuntimeError("a bounded wait on a peer expired (status %d)" % st)
     if getattr(wk, "comm", None) is not None:
         torch.cuda.synchronize()
         pplb200.nccl_comm_destroy(wk.comm)
@@ -579,6 +627,8 @@ def main():
     ap.add_argument("--workload", default="c1")
     ap.add_argument("--extras", action="store_true", help="also run the other configurations (sharded where they shard)")
     ap.add_argument("--aux", action="store_true", help="also time the quantizer and the RMSNorm+quantize producer alone")
+    ap.add_argument("--row-reduce", default="p2p", choices=["p2p", "nccl"],
+                    help="reduction of the row-parallel linear: over peer-mapped memory (default) or NCCL collectives")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     args = ap.parse_args()

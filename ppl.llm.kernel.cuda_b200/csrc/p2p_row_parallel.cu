@@ -35,7 +35,9 @@ namespace pplb200 {
 namespace {
 
 constexpr int64_t kFlagBytes = 4096;
-constexpr int kStatusWord = 64;         // uint32 index inside the flag page
+constexpr int kStatusWord = 64;         // uint32 indices inside the flag page
+constexpr int kEpochWord = 65;          // number of produce phases enqueued so far; advanced on the device,
+                                        // so a captured graph of the operation can be replayed
 constexpr long long kPeerWaitCycles = 4000000000LL;
 constexpr unsigned ST_WAIT_PARTIALS = 1u, ST_WAIT_ROWS = 2u;
 
@@ -46,7 +48,6 @@ struct Ctx {
     uint8_t* peer[kMaxPeers] = {};
     bool opened[kMaxPeers] = {};
     bool connected = false;
-    uint32_t epoch = 0;
 };
 
 struct Peers {
@@ -70,20 +71,30 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
     return v;
 }
 
-// flags[phase][src] of every peer <- epoch.  Launched after the kernel whose stores it publishes.
-__global__ void p2p_signal_kernel(Peers pr, int phase, uint32_t epoch) {
+// flags[phase][src] of every peer <- epoch.  Launched after the kernel whose stores it publishes;
+// the produce phase (0) advances this rank's epoch first.
+__global__ void p2p_signal_kernel(Peers pr, int phase) {
+    __shared__ uint32_t epoch_s;
     const int t = threadIdx.x;
+    if (t == 0) {
+        uint32_t* mine = reinterpret_cast<uint32_t*>(pr.base[pr.rank]) + kEpochWord;
+        uint32_t e = *reinterpret_cast<volatile uint32_t*>(mine);
+        if (phase == 0) *reinterpret_cast<volatile uint32_t*>(mine) = ++e;
+        epoch_s = e;
+    }
+    __syncthreads();
     if (t < pr.size) {
         __threadfence_system();
-        st_release_sys(reinterpret_cast<uint32_t*>(pr.base[t]) + phase * kMaxPeers + pr.rank, epoch);
+        st_release_sys(reinterpret_cast<uint32_t*>(pr.base[t]) + phase * kMaxPeers + pr.rank, epoch_s);
     }
 }
 
-// Block-wide: returns when every rank's flag of `phase` has reached `epoch`, or when the cycle
+// Block-wide: returns when every rank's flag of `phase` has reached this rank's epoch, or when the cycle
 // budget is spent (status |= code), or at once when the status word is already set.
-__device__ __forceinline__ void wait_flags(uint32_t* flag_page, int phase, int size, uint32_t epoch, unsigned code) {
+__device__ __forceinline__ void wait_flags(uint32_t* flag_page, int phase, int size, unsigned code) {
     if ((int)threadIdx.x < size) {
         uint32_t* status = flag_page + kStatusWord;
+        const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(flag_page + kEpochWord);
         const uint32_t* f = flag_page + phase * kMaxPeers + threadIdx.x;
         if (*reinterpret_cast<volatile uint32_t*>(status) == 0) {
             const long long t0 = clock64();
@@ -101,11 +112,11 @@ __device__ __forceinline__ void wait_flags(uint32_t* flag_page, int phase, int s
 // Sums the `size` partial slices of this rank's rows and applies the dequant epilogue:
 // 8 columns per item.  Writes the rows into the caller's output and into the staging copy.
 __global__ void __launch_bounds__(256)
-p2p_reduce_dequant_kernel(uint32_t* flag_page, int size, uint32_t epoch, const int32_t* __restrict__ recv,
+p2p_reduce_dequant_kernel(uint32_t* flag_page, int size, const int32_t* __restrict__ recv,
                           int64_t rows, int64_t dim, const half* __restrict__ scale_m, const half* __restrict__ scale_n,
                           const half* __restrict__ bias, float down_m, float down_n, half* __restrict__ out_rows,
                           half* __restrict__ staging) {
-    wait_flags(flag_page, 0, size, epoch, ST_WAIT_PARTIALS);
+    wait_flags(flag_page, 0, size, ST_WAIT_PARTIALS);
     const int64_t chunks_per_row = dim >> 3;
     const int64_t total = rows * chunks_per_row;
     const int64_t slice = rows * dim;
@@ -150,8 +161,8 @@ p2p_reduce_dequant_kernel(uint32_t* flag_page, int size, uint32_t epoch, const i
 // Work is cut into 4 KiB pieces (256 threads x 16 bytes); consecutive pieces read different peers,
 // starting with rank + 1, so all links carry traffic at once and no two ranks start on the same peer.
 __global__ void __launch_bounds__(256)
-p2p_gather_kernel(Peers pr, uint32_t epoch, int64_t staging_offset, int64_t rows, int64_t dim, half* __restrict__ out) {
-    wait_flags(reinterpret_cast<uint32_t*>(pr.base[pr.rank]), 1, pr.size, epoch, ST_WAIT_ROWS);
+p2p_gather_kernel(Peers pr, int64_t staging_offset, int64_t rows, int64_t dim, half* __restrict__ out) {
+    wait_flags(reinterpret_cast<uint32_t*>(pr.base[pr.rank]), 1, pr.size, ST_WAIT_ROWS);
     const int others = pr.size - 1;
     const int64_t vec_per_slice = rows * dim >> 3;
     const int64_t pieces = ((vec_per_slice + 255) >> 8) * others;
@@ -323,7 +334,6 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx
     uint32_t* flag_page = reinterpret_cast<uint32_t*>(c->base);
 
     if (phases & 1) {
-        c->epoch += 1;
         GemmArgs g;
         g.A = (const int8_t*)input; g.lda = lda; g.B = (const int8_t*)weight; g.ldb = Kw;
         g.M = M; g.N = N; g.K = Kw; g.mode = EPI_PUSH_I32;
@@ -335,21 +345,21 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx
         g.push_rows = (int32_t)Ms; g.push_rank = rank;
         const int32_t rc = launch_gemm(stream, g);
         if (rc != RC_SUCCESS) return rc;
-        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, 0, c->epoch);
+        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, 0);
     }
     if (phases & 2) {
         int64_t blocks = (Ms * (N >> 3) + 255) / 256;
         if (blocks > 148 * 8) blocks = 148 * 8;
         p2p_reduce_dequant_kernel<<<(unsigned)blocks, 256, 0, stream>>>(
-            flag_page, size, c->epoch, reinterpret_cast<const int32_t*>(c->base + recv_off), Ms, N,
+            flag_page, size, reinterpret_cast<const int32_t*>(c->base + recv_off), Ms, N,
             (const half*)scale_M + (int64_t)rank * Ms, (const half*)scale_N, (const half*)optional_bias, down_scale_M,
             down_scale_N, (half*)output + (int64_t)rank * Ms * N, reinterpret_cast<half*>(c->base + staging_off));
-        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, 1, c->epoch);
+        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, 1);
     }
     if ((phases & 4) && size > 1) {
         int64_t blocks = ((Ms * N >> 3) + 255) / 256 * (size - 1);
         if (blocks > 148 * 8) blocks = 148 * 8;
-        p2p_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(pr, c->epoch, staging_off, Ms, N, (half*)output);
+        p2p_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(pr, staging_off, Ms, N, (half*)output);
     }
     return check_launch("row_parallel_linear_p2p");
 }

@@ -2,6 +2,8 @@
 
 Needs >= 2 CUDA devices; skipped otherwise.  Checks, bit for bit, that
   * the row-parallel linear with the exact int32 reduction equals the unsharded fused linear,
+  * the row-parallel linear over peer-mapped memory (inter-process handles, no collective library on
+    the data path) equals it too, call after call on the same buffers,
   * the column-parallel linear with gather_output equals the unsharded fused linear,
 and that the reference-order fp16 reduction stays within a few ulp of the exact result."""
 import os
@@ -36,6 +38,25 @@ def _worker(rank, world, tmp):
         time.sleep(0.05)
     comm = pplb200.nccl_comm_init(open(uid_path, "rb").read(), rank, world)
 
+    def file_barrier(tag):
+        open(os.path.join(tmp, "%s.%d" % (tag, rank)), "w").close()
+        t1 = time.time()
+        while not all(os.path.exists(os.path.join(tmp, "%s.%d" % (tag, r))) for r in range(world)):
+            if time.time() - t1 > 120:
+                raise RuntimeError("rank %d: barrier %s timed out" % (rank, tag))
+            time.sleep(0.02)
+
+    p2p = pplb200.P2PContext(rank, world, 1024, 1536)
+    with open(os.path.join(tmp, "p2p%d.tmp" % rank), "wb") as f:
+        f.write(p2p.handle())
+    os.rename(os.path.join(tmp, "p2p%d.tmp" % rank), os.path.join(tmp, "p2p%d" % rank))
+    t0 = time.time()
+    while not all(os.path.exists(os.path.join(tmp, "p2p%d" % r)) for r in range(world)):
+        if time.time() - t0 > 120:
+            raise RuntimeError("rank %d: peer handles missing" % rank)
+        time.sleep(0.02)
+    p2p.connect([open(os.path.join(tmp, "p2p%d" % r), "rb").read() for r in range(world)])
+
     rng = np.random.default_rng(123)  # same inputs on every rank
     results = {}
     for (M, K, N) in [(64, 1024, 512), (300, 2048, 1536), (1024, 1024, 768), (33, 512, 256)]:  # chunked / odd-M paths too
@@ -51,6 +72,13 @@ def _worker(rank, world, tmp):
                                             rank=rank, size=world, comm=comm)
         y_ref_order = pplb200.row_parallel_linear(xq[:, k0:k1], w[:, k0:k1].contiguous(), sm, sn, bias, K, N,
                                                   rank=rank, size=world, comm=comm, reduce_mode=1)
+        if M % world == 0:
+            w_shard = w[:, k0:k1].contiguous()
+            ok_p2p = True
+            for _ in range(3):  # the same peer buffers, three calls in a row
+                y_p2p = pplb200.row_parallel_linear_p2p(p2p, xq[:, k0:k1], w_shard, sm, sn, bias, K, N)
+                ok_p2p = ok_p2p and bool(torch.equal(y_p2p.view(torch.int16), full.view(torch.int16)))
+            results["%dx%dx%d row p2p exact" % (M, K, N)] = ok_p2p
         n0, n1 = wl.shard_rows(N, world, rank)
         gather = torch.empty((world, M, n1 - n0), dtype=torch.float16, device="cuda")
         y_col = pplb200.column_parallel_linear(xq, w[n0:n1].contiguous(), sm, sn[n0:n1].contiguous(),
@@ -63,7 +91,10 @@ def _worker(rank, world, tmp):
         err = (y_ref_order.float() - full.float()).abs().max().item()
         scale = full.float().abs().max().item()
         results[key + " fp16-order close"] = bool(err <= 4e-3 * scale + 1e-3)
-    ok = pplb200.gemm_status() == 0
+    ok = pplb200.gemm_status() == 0 and p2p.status() == 0
+    torch.cuda.synchronize()
+    file_barrier("p2p_done")  # no rank unmaps its buffer while a peer may still read it
+    p2p.destroy()
     pplb200.nccl_comm_destroy(comm)
     with open(os.path.join(tmp, "rank%d" % rank), "w") as f:
         f.write(repr((ok, results)))
