@@ -260,7 +260,7 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream, const void* in
  * `phases`: 7 for the whole operation.  The bits (1 produce, 2 reduce, 4 gather) let one process
  * that drives several ranks on one stream enqueue the phases rank after rank.
  * Waits on peers are bounded (about two seconds); pplb200_p2p_status returns a non-zero word
- * when one expired (bit 0: partial sums missing, bit 1: finished rows missing) -- the output of
+ * when one expired (bit 0: partial sums missing, bit 1: finished rows missing, bit 2: row maxima missing) -- the output of
  * that call is then undefined and later calls do not wait until the word is reset.
  */
 int64_t pplb200_i8i8_row_parallel_p2p_bytes(int64_t M, int64_t out_features, int32_t size);
@@ -276,6 +276,23 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream, void* ctx,
                                              float down_scale_M, float down_scale_N,
                                              int64_t in_features, int64_t out_features,
                                              int32_t phases, void* output);
+
+/*
+ * Per-token quantizer for activations that are sharded along the quantized dimension (the input
+ * of a row-parallel linear as the preceding column-parallel operator leaves it): every rank passes
+ * its shard [batch, shard_dim] fp16, dense.  The row scale comes from the maximum over the WHOLE
+ * row: the ranks exchange their shard maxima through the peer-mapped buffer of `ctx` inside the
+ * kernel, so int8 values and scales equal those of pplb200_i8i8_minmax_quantize_fp16 on the
+ * unsharded rows (src/ppl/kernel/llm/cuda/pmx/i8i8/quantize.cu:27-124), bit for bit, while each
+ * rank reads only its shard, once.  `scale` [batch] is the full-row scale on every rank.
+ * batch <= 16384, shard_dim % 16 == 0, shard_dim <= 32768; all ranks call it with the same batch,
+ * in the same order on their contexts.  phases: 3 for the operation; 1 only publishes the shard
+ * maxima (lets one process that drives several ranks on one stream run "1" for every rank and then
+ * "3" for every rank).  A wait that expires sets bit 2 of pplb200_p2p_status.
+ */
+int32_t pplb200_i8i8_minmax_quantize_fp16_p2p(pplb200_stream_t stream, void* ctx, const void* input, int64_t batch,
+                                              int64_t shard_dim, float up_scale, int32_t phases,
+                                              void* q, void* scale);
 
 /*
  * NCCL plumbing for callers that do not already own a communicator (tests, bench).

@@ -5,7 +5,7 @@
 // other ranks fetch the finished fp16 rows.
 //
 //   rank r, rows [r * Ms, (r + 1) * Ms), Ms = M / size
-//   buffer of every rank:  | flags 4 KiB | recv int32 [size][Ms][N] | staging fp16 [Ms][N] |
+//   buffer of every rank:  | flags 4 KiB | row-maximum slots 2 MiB | recv int32 [size][Ms][N] | staging fp16 [Ms][N] |
 //
 //   produce : GEMM (K shard) -> tile rows of owner o go to  peer[o].recv[r]           (remote stores)
 //             signal(0)      -> peer[*].flags[0][r] = epoch                           (release, system scope)
@@ -26,6 +26,7 @@
 // Every wait is bounded; on expiry a code is ORed into the context's status word, later waits
 // of that context return at once, and the result is undefined until the status is cleared.
 #include "common.cuh"
+#include "quant_device.cuh"
 #include "../../include/pplb200_i8i8.h"
 
 #include <new>
@@ -39,7 +40,11 @@ constexpr int kStatusWord = 64;         // uint32 indices inside the flag page
 constexpr int kEpochWord = 65;          // number of produce phases enqueued so far; advanced on the device,
                                         // so a captured graph of the operation can be replayed
 constexpr long long kPeerWaitCycles = 4000000000LL;
-constexpr unsigned ST_WAIT_PARTIALS = 1u, ST_WAIT_ROWS = 2u;
+constexpr int kQuantEpochWord = 66;     // number of sharded-quantizer calls completed
+constexpr int kQuantDoneWord = 67;      // CTAs of the running sharded quantizer that have finished
+constexpr int64_t kQuantMaxRows = 16384;
+constexpr int64_t kSlotBytes = 2 * kMaxPeers * kQuantMaxRows * 8; // [parity][source rank][row] of {epoch, max|x| bits}
+constexpr unsigned ST_WAIT_PARTIALS = 1u, ST_WAIT_ROWS = 2u, ST_WAIT_ROW_MAX = 4u;
 
 struct Ctx {
     int32_t rank = 0, size = 1, device = 0;
@@ -177,6 +182,116 @@ p2p_gather_kernel(Peers pr, int64_t staging_offset, int64_t rows, int64_t dim, h
     }
 }
 
+// ---- sharded per-token quantizer ------------------------------------------------------------
+// Every rank holds the K shard [batch, dim] of the activation rows; the row scale must come from the
+// maximum over the whole row.  Persistent kernel, all CTAs resident, one row per CTA iteration: the
+// row is loaded into registers once, its shard maximum is published to every rank as one 8-byte
+// word {epoch, float bits} (a single store, so no ordering is needed), the CTA polls its own slots
+// until every rank's word of this epoch has arrived, and rounds the row with the global maximum --
+// the same arithmetic as the unsharded quantizer, hence the same int8 values and scales.
+// A CTA publishes a row before it waits for it, and every CTA of the grid is resident, so the ranks
+// cannot block one another.  Slots alternate between two banks by epoch parity: a rank can only
+// reach epoch e + 2 after every peer finished epoch e + 1, i.e. after it read all words of epoch e.
+using namespace qdev;
+
+__device__ __forceinline__ void st_relaxed_sys_u64(unsigned long long* p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_relaxed_sys_u64(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+template <int UNITS>
+__global__ void __launch_bounds__(QTPB)
+p2p_quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim, float up_scale,
+                         int8_t* __restrict__ q, half* __restrict__ scale_out, Peers pr, int publish_only) {
+    __shared__ float red[QTPB / 32];
+    __shared__ uint32_t epoch_s;
+    __shared__ float row_max_s;
+    uint32_t* flag_page = reinterpret_cast<uint32_t*>(pr.base[pr.rank]);
+    uint32_t* status = flag_page + kStatusWord;
+    if (threadIdx.x == 0) epoch_s = *reinterpret_cast<volatile uint32_t*>(flag_page + kQuantEpochWord) + 1u;
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    const int64_t bank = (int64_t)(epoch & 1u) * kMaxPeers * kQuantMaxRows;
+    const int units = (int)(dim >> 4);
+
+    for (int64_t row = blockIdx.x; row < batch; row += gridDim.x) {
+        const uint4* src = reinterpret_cast<const uint4*>(in + row * dim);
+        uint4 v[UNITS][2];
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const int unit = u * blockDim.x + threadIdx.x;
+            if (unit < units) {
+                v[u][0] = ldg_stream(src + 2 * unit);
+                v[u][1] = ldg_stream(src + 2 * unit + 1);
+            } else {
+                v[u][0] = make_uint4(0, 0, 0, 0);
+                v[u][1] = make_uint4(0, 0, 0, 0);
+            }
+        }
+        __half2 m2 = __float2half2_rn(0.0f);
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const __half2* h = reinterpret_cast<const __half2*>(&v[u][0]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) m2 = __hmax2(m2, __habs2(h[i]));
+        }
+        const float shard_max = block_max(fmaxf(__low2float(m2), __high2float(m2)), red, blockDim.x >> 5);
+
+        if (threadIdx.x < 32) {
+            float other = 0.0f;
+            if ((int)threadIdx.x < pr.size) {
+                const int peer = threadIdx.x;
+                unsigned long long* theirs = reinterpret_cast<unsigned long long*>(pr.base[peer] + kFlagBytes) + bank + (int64_t)pr.rank * kQuantMaxRows + row;
+                st_relaxed_sys_u64(theirs, ((unsigned long long)epoch << 32) | __float_as_uint(shard_max));
+                const unsigned long long* mine = reinterpret_cast<const unsigned long long*>(pr.base[pr.rank] + kFlagBytes) + bank + (int64_t)peer * kQuantMaxRows + row;
+                unsigned long long w = ld_relaxed_sys_u64(mine);
+                if (!publish_only && (uint32_t)(w >> 32) != epoch && *reinterpret_cast<volatile uint32_t*>(status) == 0) {
+                    const long long t0 = clock64();
+                    for (uint32_t spin = 1;; ++spin) {
+                        w = ld_relaxed_sys_u64(mine);
+                        if ((uint32_t)(w >> 32) == epoch) break;
+                        if ((spin & 0xffu) == 0) {
+                            if (clock64() - t0 > kPeerWaitCycles) { atomicOr(status, ST_WAIT_ROW_MAX); break; }
+                            if (*reinterpret_cast<volatile uint32_t*>(status) != 0) break;
+                        }
+                    }
+                }
+                other = __uint_as_float((uint32_t)w);
+            }
+#pragma unroll
+            for (int m = 4; m >= 1; m >>= 1) other = fmaxf(other, __shfl_xor_sync(0xffffffffu, other, m));
+            if (threadIdx.x == 0) row_max_s = other;
+        }
+        __syncthreads();
+        if (publish_only) continue; // block-uniform; the next row's block_max synchronises before red[] is reused
+        const float amax = row_max_s;
+        const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-7f);
+        const float inv_scale = __frcp_rn(scale);
+#pragma unroll
+        for (int u = 0; u < UNITS; ++u) {
+            const int unit = u * blockDim.x + threadIdx.x;
+            if (unit < units)
+                *reinterpret_cast<uint4*>(q + row * dim + ((int64_t)unit << 4)) =
+                    quant16(reinterpret_cast<const __half2*>(&v[u][0]), scale, inv_scale);
+        }
+        if (threadIdx.x == 0) scale_out[row] = __float2half_rn(scale * up_scale);
+        __syncthreads(); // red[] and row_max_s are reused by the next row
+    }
+
+    // the last CTA to finish closes the epoch
+    if (threadIdx.x == 0 && !publish_only) {
+        __threadfence();
+        if (atomicAdd(flag_page + kQuantDoneWord, 1u) == gridDim.x - 1) {
+            flag_page[kQuantDoneWord] = 0u;
+            *reinterpret_cast<volatile uint32_t*>(flag_page + kQuantEpochWord) = epoch;
+        }
+    }
+}
+
 int64_t recv_bytes(int64_t M, int64_t N) { return round_up(M * N * 4, 256); }
 int64_t staging_bytes(int64_t M, int64_t N, int32_t size) { return round_up(M / size * N * 2, 256); }
 
@@ -196,14 +311,14 @@ extern "C" {
 
 int64_t pplb200_i8i8_row_parallel_p2p_bytes(int64_t M, int64_t N, int32_t size) {
     if (M < 0 || N < 0 || size < 1 || size > kMaxPeers) return -1;
-    return kFlagBytes + recv_bytes(M, N) + staging_bytes(M, N, size);
+    return kFlagBytes + kSlotBytes + recv_bytes(M, N) + staging_bytes(M, N, size);
 }
 
 int32_t pplb200_p2p_create(int32_t rank, int32_t size, int64_t bytes, void** ctx_out) {
     clear_error();
     if (!ctx_out) return fail(RC_INVALID_VALUE, "ctx_out is null");
     if (size < 1 || size > kMaxPeers || rank < 0 || rank >= size) return fail(RC_INVALID_VALUE, "bad rank/size %d/%d", rank, size);
-    if (bytes < kFlagBytes) return fail(RC_INVALID_VALUE, "buffer smaller than the flag page");
+    if (bytes < kFlagBytes + kSlotBytes) return fail(RC_INVALID_VALUE, "buffer smaller than the flag and slot pages");
     Ctx* c = new (std::nothrow) Ctx;
     if (!c) return fail(RC_DEVICE_RUNTIME_ERROR, "out of host memory");
     c->rank = rank; c->size = size; c->bytes = bytes;
@@ -212,10 +327,10 @@ int32_t pplb200_p2p_create(int32_t rank, int32_t size, int64_t bytes, void** ctx
         delete c;
         return rc;
     }
-    if (cudaMemset(c->base, 0, (size_t)kFlagBytes) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+    if (cudaMemset(c->base, 0, (size_t)(kFlagBytes + kSlotBytes)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
         cudaFree(c->base);
         delete c;
-        return fail(RC_DEVICE_RUNTIME_ERROR, "clearing the flag page failed");
+        return fail(RC_DEVICE_RUNTIME_ERROR, "clearing the flag and slot pages failed");
     }
     c->peer[rank] = c->base;
     c->connected = size == 1;
@@ -329,7 +444,7 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx
         return fail(RC_INVALID_VALUE, "peer buffer too small for M=%lld N=%lld", (long long)M, (long long)N);
     if (M == 0 || N == 0) return RC_SUCCESS;
 
-    const int64_t recv_off = kFlagBytes, staging_off = kFlagBytes + recv_bytes(M, N);
+    const int64_t recv_off = kFlagBytes + kSlotBytes, staging_off = recv_off + recv_bytes(M, N);
     const Peers pr = peers_of(*c);
     uint32_t* flag_page = reinterpret_cast<uint32_t*>(c->base);
 
@@ -362,6 +477,54 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx
         p2p_gather_kernel<<<(unsigned)blocks, 256, 0, stream>>>(pr, staging_off, Ms, N, (half*)output);
     }
     return check_launch("row_parallel_linear_p2p");
+}
+
+} // extern "C"
+
+template <int UNITS>
+static int32_t launch_p2p_quantize(cudaStream_t stream, const Ctx& c, const half* in, int64_t batch, int64_t dim,
+                                   float up_scale, int8_t* q, half* scale, int threads, int publish_only) {
+    int per_sm = 0, sms = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, p2p_quantize_rows_kernel<UNITS>, threads, 0) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c.device) != cudaSuccess || per_sm < 1)
+        return fail(RC_DEVICE_RUNTIME_ERROR, "occupancy query failed");
+    int64_t grid = (int64_t)per_sm * sms; // every CTA resident: none waits for an SM while its row is awaited elsewhere
+    if (grid > batch) grid = batch;
+    p2p_quantize_rows_kernel<UNITS><<<(unsigned)grid, threads, 0, stream>>>(in, batch, dim, up_scale, q, scale, peers_of(c), publish_only);
+    return check_launch("minmax_quantize_fp16_p2p");
+}
+
+extern "C" {
+
+int32_t pplb200_i8i8_minmax_quantize_fp16_p2p(pplb200_stream_t stream_, void* ctx, const void* input, int64_t batch,
+                                              int64_t shard_dim, float up_scale, int32_t phases, void* q, void* scale) {
+    clear_error();
+    cudaStream_t stream = (cudaStream_t)stream_;
+    Ctx* c = (Ctx*)ctx;
+    if (!c) return fail(RC_INVALID_VALUE, "null context");
+    if (!c->connected) return fail(RC_INVALID_VALUE, "context is not connected to its peers");
+    if (batch < 0 || shard_dim < 0) return fail(RC_INVALID_VALUE, "negative extent");
+    if (phases != 1 && phases != 3) return fail(RC_INVALID_VALUE, "phases must be 3 (whole operation) or 1 (publish the shard maxima only)");
+    const int publish_only = phases == 1;
+    if (batch > kQuantMaxRows) return fail(RC_UNSUPPORTED, "more than %lld rows", (long long)kQuantMaxRows);
+    if (shard_dim % 16) return fail(RC_UNSUPPORTED, "shard_dim %% 16 != 0");
+    const int64_t units = shard_dim >> 4;
+    if (units > (int64_t)QTPB * 8) return fail(RC_UNSUPPORTED, "shard rows longer than %d elements", QTPB * 8 * 16);
+    if (batch == 0 || shard_dim == 0) return RC_SUCCESS;
+    if (!input || !q || !scale) return fail(RC_INVALID_VALUE, "null pointer argument");
+    if (!aligned16(input) || !aligned16(q)) return fail(RC_INVALID_VALUE, "input and output must be 16-byte aligned");
+    const int per = (int)((units + QTPB - 1) / QTPB);
+    const int bucket = per <= 1 ? 1 : per <= 2 ? 2 : per <= 4 ? 4 : 8;
+    int threads = (int)((units + bucket - 1) / bucket);
+    threads = (threads + 31) / 32 * 32;
+    if (threads > QTPB) threads = QTPB;
+    const half* in = (const half*)input;
+    switch (bucket) {
+    case 1: return launch_p2p_quantize<1>(stream, *c, in, batch, shard_dim, up_scale, (int8_t*)q, (half*)scale, threads, publish_only);
+    case 2: return launch_p2p_quantize<2>(stream, *c, in, batch, shard_dim, up_scale, (int8_t*)q, (half*)scale, threads, publish_only);
+    case 4: return launch_p2p_quantize<4>(stream, *c, in, batch, shard_dim, up_scale, (int8_t*)q, (half*)scale, threads, publish_only);
+    default: return launch_p2p_quantize<8>(stream, *c, in, batch, shard_dim, up_scale, (int8_t*)q, (half*)scale, threads, publish_only);
+    }
 }
 
 }

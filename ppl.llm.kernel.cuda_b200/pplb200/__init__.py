@@ -40,6 +40,7 @@ EXPORTS = [
     "pplb200_i8i8_gate_up_swiglu_workspace_bytes", "pplb200_i8i8_gate_up_swiglu_requant",
     "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
     "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
+    "pplb200_i8i8_minmax_quantize_fp16_p2p",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -86,6 +87,7 @@ def _load():
     lib.pplb200_p2p_destroy.argtypes = [vp]
     lib.pplb200_p2p_status.argtypes = [vp, i32]
     lib.pplb200_i8i8_row_parallel_linear_p2p.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32, vp]
+    lib.pplb200_i8i8_minmax_quantize_fp16_p2p.argtypes = [vp, vp, vp, i64, i64, f32, i32, vp, vp]
     lib.pplb200_nccl_get_unique_id.argtypes = [vp]
     lib.pplb200_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
     lib.pplb200_nccl_comm_destroy.argtypes = [vp]
@@ -401,3 +403,17 @@ def row_parallel_linear_p2p(p2p, xq, w, scale_m, scale_n, bias, in_features, out
                                                     _ptr(scale_m), _ptr(scale_n), down_m, down_n, in_features,
                                                     out_features, phases, _ptr(out)))
     return out
+
+
+def minmax_quantize_fp16_p2p(p2p, x_shard, up_scale=TOKEN_UP_SCALE, out=None, scale=None, phases=3):
+    """Quantizes this rank's K shard [M, K / size] with the row scale of the whole row."""
+    import torch
+    M, Kw = x_shard.shape
+    assert x_shard.is_contiguous()
+    if out is None:
+        out = torch.empty((M, Kw), dtype=torch.int8, device=x_shard.device)
+    if scale is None:
+        scale = torch.empty((M,), dtype=torch.float16, device=x_shard.device)
+    _check(lib.pplb200_i8i8_minmax_quantize_fp16_p2p(_stream(), p2p.ctx, _ptr(x_shard), M, Kw, up_scale, phases,
+                                                     _ptr(out), _ptr(scale)))
+    return out, scale

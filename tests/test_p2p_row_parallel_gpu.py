@@ -115,3 +115,47 @@ def test_p2p_wait_gives_up_and_reports(cuda, pplb200):
     finally:
         a.destroy()
         b.destroy()
+
+
+@pytest.mark.parametrize("world,M,K", [
+    (2, 64, 1024),       # 512-element shards: one unit per thread, partial block
+    (4, 300, 8192),      # 2048-element shards
+    (8, 2048, 28672),    # the row-parallel workload's shape: 3584-element shards, more rows than resident CTAs
+    (2, 16, 65536),      # 32768-element shards: eight units per thread
+    (3, 50, 3 * 400 * 16),
+    (1, 40, 512),
+])
+def test_sharded_quantizer_matches_unsharded(cuda, pplb200, world, M, K):
+    """Shard maxima are published for every rank first (phase 1), then every rank runs the whole
+    operation (phase 3), so no kernel waits for one that has not run.  int8 and scales bit-exact."""
+    torch = cuda
+    from pplb200 import workloads as wl
+    rng = np.random.default_rng(M + K + world)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    x[:, rng.integers(0, K, 8)] *= 30.0   # the row maximum usually sits in one shard only
+    if M > 3:
+        x[3] = 0.0                         # an all-zero row: scale clamps to 1e-7
+    x = torch.from_numpy(x).cuda()
+    q_full, s_full = pplb200.minmax_quantize_fp16(x)
+    ctxs = [pplb200.P2PContext(r, world, M, 64) for r in range(world)]
+    try:
+        for c in ctxs:
+            c.connect_local(ctxs)
+        for rounds in range(3):  # both slot banks, and a bank's reuse
+            shards, outs = [], []
+            for r in range(world):
+                k0, k1 = wl.shard_rows(K, world, r)
+                shards.append(x[:, k0:k1].contiguous())
+            for r in range(world):
+                pplb200.minmax_quantize_fp16_p2p(ctxs[r], shards[r], phases=1)
+            for r in range(world):
+                outs.append(pplb200.minmax_quantize_fp16_p2p(ctxs[r], shards[r]))
+            torch.cuda.synchronize()
+            for r in range(world):
+                k0, k1 = wl.shard_rows(K, world, r)
+                assert ctxs[r].status() == 0
+                assert torch.equal(outs[r][1].view(torch.int16), s_full.view(torch.int16)), "scales, rank %d" % r
+                assert torch.equal(outs[r][0], q_full[:, k0:k1]), "int8, rank %d" % r
+    finally:
+        for c in ctxs:
+            c.destroy()
