@@ -259,6 +259,9 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream, const void* in
  * rank when the call's work on `stream` has finished.
  * `phases`: 7 for the whole operation.  The bits (1 produce, 2 reduce, 4 gather) let one process
  * that drives several ranks on one stream enqueue the phases rank after rank.
+ * With 7, large problems on four or more ranks are cut into two column chunks and the reduction and
+ * row exchange of the first chunk run on a second stream (owned by the context) under the GEMM of the
+ * second; 7 + 8 forces that schedule where the shape allows it, 7 + 16 forces the single-chunk one.
  * Waits on peers are bounded (about two seconds); pplb200_p2p_status returns a non-zero word
  * when one expired (bit 0: partial sums missing, bit 1: finished rows missing, bit 2: row maxima missing) -- the output of
  * that call is then undefined and later calls do not wait until the word is reset.

@@ -46,7 +46,7 @@ def _worker(rank, world, tmp):
                 raise RuntimeError("rank %d: barrier %s timed out" % (rank, tag))
             time.sleep(0.02)
 
-    p2p = pplb200.P2PContext(rank, world, 1024, 1536)
+    p2p = pplb200.P2PContext(rank, world, 2048, 8192)
     with open(os.path.join(tmp, "p2p%d.tmp" % rank), "wb") as f:
         f.write(p2p.handle())
     os.rename(os.path.join(tmp, "p2p%d.tmp" % rank), os.path.join(tmp, "p2p%d" % rank))
@@ -59,7 +59,8 @@ def _worker(rank, world, tmp):
 
     rng = np.random.default_rng(123)  # same inputs on every rank
     results = {}
-    for (M, K, N) in [(64, 1024, 512), (300, 2048, 1536), (1024, 1024, 768), (33, 512, 256)]:  # chunked / odd-M paths too
+    # the last shape is large enough for the peer-memory path's two-chunk schedule (second stream)
+    for (M, K, N) in [(64, 1024, 512), (300, 2048, 1536), (1024, 1024, 768), (33, 512, 256), (2048, 2048, 8192)]:
         x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float16)).cuda()
         w = torch.from_numpy(rng.integers(-127, 128, (N, K), dtype=np.int8)).cuda()
         sn = torch.from_numpy((rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)).cuda()
@@ -85,6 +86,9 @@ def _worker(rank, world, tmp):
             for _ in range(3):  # the same peer buffers, three calls in a row
                 y_p2p = pplb200.row_parallel_linear_p2p(p2p, xq[:, k0:k1], w_shard, sm, sn, bias, K, N)
                 ok_p2p = ok_p2p and bool(torch.equal(y_p2p.view(torch.int16), full.view(torch.int16)))
+                if M * N >= (4 << 20):  # the opt-in two-chunk schedule (second stream), mixed with the default one
+                    y_p2p = pplb200.row_parallel_linear_p2p(p2p, xq[:, k0:k1], w_shard, sm, sn, bias, K, N, phases=7 + 8)
+                    ok_p2p = ok_p2p and bool(torch.equal(y_p2p.view(torch.int16), full.view(torch.int16)))
             results["%dx%dx%d row p2p exact" % (M, K, N)] = ok_p2p
         n0, n1 = wl.shard_rows(N, world, rank)
         gather = torch.empty((world, M, n1 - n0), dtype=torch.float16, device="cuda")
