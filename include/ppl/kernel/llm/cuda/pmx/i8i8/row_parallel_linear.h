@@ -66,6 +66,55 @@ inline ppl::common::RetCode row_parallel_linear(
         cublas_workspace, cublas_workspace_size, output);
 }
 
+// The same operator with the reduction over peer-mapped memory instead of a collective library
+// (ranks of one NVLink domain): `p2p_context` is a context of pplb200_p2p_create that has been
+// connected to its peers; it replaces nccl_param, quant_buffer and the cuBLAS arguments.  Result
+// and argument meaning as ROW_PARALLEL_REDUCE_INT32; M must be divisible by the number of ranks
+// (RC_UNSUPPORTED otherwise: call the overload above).  No counterpart in the reference.
+inline ppl::common::RetCode row_parallel_linear(
+    const cudaStream_t stream,
+    void* p2p_context,
+    const ppl::common::TensorShape* input_shape,
+    const void* input,
+    const ppl::common::TensorShape* bias_shape,
+    const void* bias,
+    const void* scale_M,
+    const void* scale_N,
+    const float down_scale_M,
+    const float down_scale_N,
+    const int64_t in_features,
+    const int64_t out_features,
+    const void* weight,
+    void* output)
+{
+    if (bias && bias_shape->GetDataType() != ppl::common::DATATYPE_FLOAT16) {
+        LOG(ERROR) << "only support fp16 bias";
+        return ppl::common::RC_UNSUPPORTED;
+    }
+    const int64_t M = (int64_t)input_shape->CalcElementsToDimensionExcludingPadding(input_shape->GetDimCount() - 1);
+    return (ppl::common::RetCode)pplb200_i8i8_row_parallel_linear_p2p(
+        (pplb200_stream_t)stream, p2p_context, input, M, /*input_ld=*/0, weight, bias, scale_M, scale_N, down_scale_M,
+        down_scale_N, in_features, out_features, /*phases=*/7, output);
+}
+
+// Per-token quantizer for activations sharded along the quantized dimension (what the preceding
+// column-parallel operator leaves on each rank): int8 values and full-row scales equal those of
+// minmax_quantize_fp16 on the unsharded rows.  input_shape is the shard's shape [.., K / size].
+inline ppl::common::RetCode minmax_quantize_fp16_sharded(
+    const cudaStream_t stream,
+    void* p2p_context,
+    const ppl::common::TensorShape* input_shape,
+    const void* input,
+    const float up_scale,
+    void* quantized,
+    void* scale)
+{
+    const int64_t dim = input_shape->GetDim(input_shape->GetDimCount() - 1);
+    const int64_t batch = (int64_t)input_shape->CalcElementsToDimensionExcludingPadding(input_shape->GetDimCount() - 1);
+    return (ppl::common::RetCode)pplb200_i8i8_minmax_quantize_fp16_p2p((pplb200_stream_t)stream, p2p_context, input, batch,
+                                                                       dim, up_scale, /*phases=*/3, quantized, scale);
+}
+
 }}}}}}
 
 #endif

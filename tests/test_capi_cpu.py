@@ -21,7 +21,7 @@ def declared_symbols():
 def test_library_exports_every_declared_symbol():
     import pplb200
     names = declared_symbols()
-    assert len(names) >= 22
+    assert len(names) >= 32
     for n in names:
         assert hasattr(pplb200.lib, n), "missing export: " + n
     assert set(names) == set(pplb200.EXPORTS)
@@ -50,6 +50,11 @@ def test_workspace_sizes():
     assert pplb200.gemm_workspace_bytes(128, 12288, 4096, pplb200.EPI_DEQUANT_F16_REQUANT_I8) >= 128 * 4
     need = pplb200.linear_workspace_bytes(128, 12288, 4096, pplb200.EPI_DEQUANT_F16_REQUANT_I8)
     assert need >= 128 * 4096 + 128 * 2 + 128 * 4 and need % 256 == 0
+    # peer buffer of the row-parallel linear: flags + row-maximum slots + int32 partials [M, N] + fp16 rows [M / size, N]
+    b = pplb200.lib.pplb200_i8i8_row_parallel_p2p_bytes(2048, 8192, 8)
+    assert b >= 2048 * 8192 * 4 + 256 * 8192 * 2 and b % 256 == 0
+    assert pplb200.lib.pplb200_i8i8_row_parallel_p2p_bytes(2048, 8192, 9) == -1   # more ranks than one NVLink domain holds
+    assert pplb200.lib.pplb200_i8i8_row_parallel_p2p_bytes(2048, 8192, 0) == -1
 
 
 def test_reference_compatible_headers_compile(tmp_path):
@@ -97,8 +102,15 @@ ppl::common::RetCode run(cudaStream_t s, cublasLtHandle_t lt, k::cublas::AlgoCac
     rc = k::pmx::i8i8::minmax_dequantize_silu_fp16(s, qbuf, sm, sn, nullptr, nullptr, nullptr, 16, 4096,
         k::MATRIX_LAYOUT_ROW_MAJOR, k::pmx::i8i8::token_down_scale, k::pmx::i8i8::hidden_down_scale, y);
     if (rc != ppl::common::RC_SUCCESS) return rc;
-    return k::pmx::i8i8::minmax_requantize_swiglu_fp16(s, qbuf, sm, sn, 16, 2048, 1.0f, k::MATRIX_LAYOUT_ROW_MAJOR,
+    rc = k::pmx::i8i8::minmax_requantize_swiglu_fp16(s, qbuf, sm, sn, 16, 2048, 1.0f, k::MATRIX_LAYOUT_ROW_MAJOR,
         k::pmx::i8i8::token_up_scale, k::pmx::i8i8::token_down_scale, k::pmx::i8i8::hidden_down_scale, y, xq, sm);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    // additions without a reference counterpart: the peer-memory forms of the row-parallel pair
+    void* p2p = nullptr;
+    rc = k::pmx::i8i8::minmax_quantize_fp16_sharded(s, p2p, &in, x, k::pmx::i8i8::token_up_scale, xq, sm);
+    if (rc != ppl::common::RC_SUCCESS) return rc;
+    return k::pmx::i8i8::row_parallel_linear(s, p2p, &in, xq, &b, bias, sm, sn, k::pmx::i8i8::token_down_scale,
+        k::pmx::i8i8::hidden_down_scale, 4096, 4096, w, y);
 }
 int main() {
     k::MatrixLayoutHelper<k::MATRIX_LAYOUT_COL32> h;
