@@ -173,7 +173,7 @@ def test_gemm_raw_i32(cuda, oracle, M, N, K):
 DECODE_SHAPES = [(128, 6272, 2048), (100, 12288, 4096), (64, 8192, 1024), (72, 3200, 512), (128, 12288, 1024), (40, 4096, 4096)]
 
 
-@pytest.mark.parametrize("M,N,K", DECODE_SHAPES)
+@pytest.mark.parametrize("M,N,K", DECODE_SHAPES + [(16, 4096, 4096), (128, 19072, 1024), (8, 1024, 256), (1, 2048, 8192)])
 def test_decode_gemm_all_modes(cuda, oracle, M, N, K):
     """Small-batch kernel across its variants: one or two weight-row tiles per CTA, K split over clusters of
     different sizes, an odd number of weight-row tiles, token counts that are not multiples of 8."""
