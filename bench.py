@@ -339,6 +339,14 @@ def build_ours(wk):
             y_host.copy_(y, non_blocking=True)
 
         h2d = xs_host.numel() * 2
+        # the step's parts, timed one by one with --row-pieces (phases = 1 runs the GEMM and its pushes only)
+        wk.pieces = {
+            "sharded_quantizer": lambda i: pplb200.minmax_quantize_fp16_p2p(wk.p2p, xs[i % wk.nsets], out=xq_shard, scale=sm),
+            "gemm_with_push": lambda i: pplb200.row_parallel_linear_p2p(wk.p2p, xq_shard, wk.w[i % wk.nsets], sm, wk.sn,
+                                                                        wk.bias, K, N, out=y, phases=1),
+            "linear_over_peer_memory": lambda i: pplb200.row_parallel_linear_p2p(wk.p2p, xq_shard, wk.w[i % wk.nsets], sm,
+                                                                                 wk.sn, wk.bias, K, N, out=y),
+        }
     else:
         def step(i):
             s = i % wk.nsets
@@ -539,6 +547,13 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
         line["cpu_baseline"] = {"value": line["value"], "unit": "TOPS", "cores": 0, "kind": "reference",
                                 "sample": "full workload; the reference path is CUDA-only, so its own kernels "
                                           "(compute_80 PTX JIT + cuBLASLt int8) run on the same GPU"}
+    if args.row_pieces and getattr(wk, "pieces", None):
+        pieces = {}
+        for name_, fn_ in wk.pieces.items():
+            pieces[name_ + "_us"] = _time_steps(_Eager(fn_), args.steps, args.warmup, world) / args.steps * 1e3
+        if ms_k is not None:
+            pieces["gemm_local_us"] = ms_k / args.steps * 1e3
+        line["row_parallel_pieces"] = pieces
     if ms_k is not None and rank == 0:
         kt = ms_k / args.steps * 1e-3
         if wk.cfg["bound"] == "hbm":
@@ -647,6 +662,8 @@ def main():
     ap.add_argument("--aux", action="store_true", help="also time the quantizer and the RMSNorm+quantize producer alone")
     ap.add_argument("--row-reduce", default="p2p", choices=["p2p", "nccl"],
                     help="reduction of the row-parallel linear: over peer-mapped memory (default) or NCCL collectives")
+    ap.add_argument("--row-pieces", action="store_true",
+                    help="row-parallel workload over peer memory: also time the sharded quantizer, the GEMM with its pushes and the whole linear")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     args = ap.parse_args()
