@@ -8,11 +8,13 @@
 //   buffer of every rank:  | flags 4 KiB | row-maximum slots 2 MiB | recv int32 [size][Ms][N] | staging fp16 [Ms][N] |
 //
 //   produce : GEMM (K shard) -> tile rows of owner o go to  peer[o].recv[r]           (remote stores)
-//             signal(0)      -> peer[*].flags[0][r] = epoch                           (release, system scope)
-//   reduce  : wait(0)        -> flags[0][*] >= epoch                                  (acquire, bounded)
+//             signal         -> peer[*].flags["partials"][r] = epoch                  (release, system scope)
+//   reduce  : wait           -> flags["partials"][*] >= epoch                         (acquire, bounded)
 //             recv[0] + .. + recv[size-1] -> dequant + bias -> output rows, staging
-//             signal(1)
-//   gather  : wait(1); output rows of every other rank <- peer[s].staging            (remote loads)
+//             signal         -> peer[*].flags["rows"][r] = epoch
+//   gather  : wait; output rows of every other rank <- peer[s].staging               (remote loads)
+// The sharded per-token quantizer that feeds it exchanges the row maxima through the slot area
+// (described at its kernel below).
 //
 // Same arithmetic as the unsharded fused linear (integer sums, then the three rounded products),
 // hence bit-identical to it.  Replaces, for ranks of one NVLink domain, the dequantize + fp16

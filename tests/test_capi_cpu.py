@@ -33,6 +33,22 @@ def test_no_torch_types_in_c_header():
     assert "torch" not in src.lower() and "at::" not in src and "#include <cuda" not in src
 
 
+def test_c_header_is_plain_c99(tmp_path):
+    """The boundary is a C ABI: the header compiles as strict C99 and a C program links against the library."""
+    src = tmp_path / "c_caller.c"
+    src.write_text('#include "pplb200_i8i8.h"\n#include <string.h>\n'
+                   'int main(void) {\n'
+                   '    if (strstr(pplb200_version(), "sm_100a") == 0) return 1;\n'
+                   '    if (pplb200_layout_offset(0, 4, 8, 1, 2) != 10) return 2;\n'
+                   '    if (pplb200_i8i8_row_parallel_p2p_bytes(-1, 8, 2) != -1) return 3;\n'
+                   '    return 0;\n}\n')
+    exe = tmp_path / "c_caller"
+    lib_dir = os.path.join(ROOT, "ppl.llm.kernel.cuda_b200", "lib")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I" + os.path.join(ROOT, "include"),
+                    str(src), "-o", str(exe), "-L" + lib_dir, "-lpplb200_i8i8", "-Wl,-rpath," + lib_dir], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
+
+
 @pytest.mark.parametrize("layout", [0, 1, 2, 3, 4])
 def test_layout_offsets_match_oracle(oracle, layout):
     import pplb200
