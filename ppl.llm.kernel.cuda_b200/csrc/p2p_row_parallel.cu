@@ -21,9 +21,9 @@
 // all-reduce of the reference (src/ppl/kernel/llm/cuda/pmx/i8i8/row_parallel_linear.cu:28-162).
 //
 // Buffer reuse needs no extra barrier: a rank's next produce follows its gather, which follows
-// every peer's signal(1), which follows that peer's reduce (the last reader of its recv buffer);
-// and a rank's next reduce (the next writer of its staging) follows every peer's next signal(0),
-// which follows that peer's gather (the last reader of this rank's staging).
+// every peer's "rows" signal, which follows that peer's reduce (the last reader of its recv buffer);
+// and a rank's next reduce (the next writer of its staging) follows every peer's next "partials"
+// signal, which follows that peer's gather (the last reader of this rank's staging).
 //
 // Every wait is bounded; on expiry a code is ORed into the context's status word, later waits
 // of that context return at once, and the result is undefined until the status is cleared.
