@@ -288,8 +288,11 @@ int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const v
     if (M > 0x7fffffffLL) return fail(RC_UNSUPPORTED, "M beyond 2^31 - 1");
     // the quantizer also clears the row-maximum scratch of the fused re-quantize
     uint32_t* absmax = epilogue_mode == EPI_DEQUANT_F16_REQUANT_I8 ? (uint32_t*)gws : nullptr;
+    // The quantizer itself is launched as a programmatic dependent of whatever precedes it on the stream: it
+    // touches no memory before its griddepcontrol.wait, so this only hides its launch latency (back-to-back
+    // calls of this function then overlap the tail of one call with the head of the next).
     int32_t rc = launch_quantize((cudaStream_t)stream, (const half*)x, M, K, up_scale, LAYOUT_ROW_MAJOR, (int8_t*)xq,
-                                 (half*)sm, nullptr, absmax, false);
+                                 (half*)sm, nullptr, absmax, /*pdl=*/M <= 128);
     if (rc != RC_SUCCESS) return rc;
     return gemm_entry((cudaStream_t)stream, xq, K, W, K, M, N, K, epilogue_mode, sm, scale_N, optional_bias, down_scale_M,
                       down_scale_N, requant_up_scale, gws, gemm_ws_bytes(M, epilogue_mode), y, N, y_q, y_q_scale, true);
