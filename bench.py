@@ -179,6 +179,33 @@ class _Captured:
                 i += 1
 
 
+def _round_stats(runner, nsets, reps, world):
+    """Per-step median and minimum over `reps` separately timed rounds (one round = one step on every
+    buffer set), in ms; rank-local CUDA events, max over ranks of each statistic."""
+    import torch
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(reps + 1)]
+    _barrier(world)
+    evs[0].record()
+    for r in range(reps):
+        runner.run(0, nsets)
+        evs[r + 1].record()
+    torch.cuda.synchronize()
+    per_step = sorted(evs[r].elapsed_time(evs[r + 1]) / nsets for r in range(reps))
+    med = per_step[len(per_step) // 2] if len(per_step) % 2 else 0.5 * (per_step[len(per_step) // 2 - 1] + per_step[len(per_step) // 2])
+    return _max_over_ranks(med, world), _max_over_ranks(per_step[0], world)
+
+
+class _SameSet:
+    """Replays the graph of buffer set 0 only: operands stay in L2 (the "L2-warm" figure)."""
+
+    def __init__(self, captured):
+        self.captured, self.nsets = captured, 1
+
+    def run(self, first, count):
+        for _ in range(count):
+            self.captured.single[0].replay()
+
+
 class _Eager:
     def __init__(self, fn):
         self.fn = fn
@@ -506,6 +533,11 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
     ms = _time_steps(step, args.steps, args.warmup, world)
     ms_e2e = _time_steps(e2e, args.steps, args.warmup, world)
     ms_k = _time_steps(kernel_only, args.steps, args.warmup, 1) if kernel_only else None
+    reps = max(5, min(20, args.steps // max(1, wk.nsets)))
+    med_ms, min_ms = _round_stats(step, wk.nsets, reps, world)
+    warm_ms = None
+    if use_graphs and wk.nsets > 1 and wk.cfg["bound"] == "hbm":
+        warm_ms = _time_steps(_SameSet(step), args.steps, args.warmup, world) / args.steps
     clocks = sampler.stop() if rank == 0 else None
     if impl == "ours":
         st = pplb200.gemm_status()
@@ -533,6 +565,9 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
                         ("none" if wk.shard is None else "%s-parallel over %d GPUs" % (wk.shard, world)),
             "l2": wk.l2_note,
             "launch": ("CUDA graph replay, %d steps (one per buffer set) per graph" % wk.nsets) if use_graphs else "eager launches",
+            "ms_per_step_median": med_ms, "ms_per_step_min": min_ms,
+            "ms_per_step_stat": "over %d separately timed rounds of %d step(s)" % (reps, wk.nsets),
+            "l2_warm_ms_per_step": warm_ms,  # one buffer set replayed: operands served from L2, NOT the headline
             "algorithmic_bytes_per_step": wl.algorithmic_bytes(name),
             "gb_per_s": wl.algorithmic_bytes(name) * replicas / (per_step * 1e-3) / 1e9 if wk.shard is None else None,
         },
