@@ -179,6 +179,11 @@ class _Captured:
                 i += 1
 
 
+class StatusWordSet(RuntimeError):
+    """A device status word was non-zero.  Raised from values that were max-reduced over the ranks, so every
+    rank raises it at the same place (the only exception run_config's callers may swallow and carry on after)."""
+
+
 def _round_stats(runner, nsets, reps, world):
     """Per-step median and minimum over `reps` separately timed rounds (one round = one step on every
     buffer set), in ms; rank-local CUDA events, max over ranks of each statistic."""
@@ -540,9 +545,9 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
         warm_ms = _time_steps(_SameSet(step), args.steps, args.warmup, world) / args.steps
     clocks = sampler.stop() if rank == 0 else None
     if impl == "ours":
-        st = pplb200.gemm_status()
+        st = int(_max_over_ranks(float(pplb200.gemm_status()), world))  # same verdict on every rank
         if st != 0:
-            raise RuntimeError("GEMM kernel reported a timed-out wait (status %d)" % st)
+            raise StatusWordSet("GEMM kernel reported a timed-out wait (status %d)" % st)
 
     replicas = world if (wk.shard is None and world > 1) else 1
     ops_per_step = wk.ops * replicas
@@ -612,13 +617,13 @@ def run_config(name, args, rank, world, impl, sharded, want_cpu):
         line["config"]["row_reduce"] = ("activations quantized shard by shard (row maxima exchanged in the kernel), int32 tiles pushed to the row owner over peer-mapped memory, fp16 rows fetched back"
                                         if wk.row_reduce == "p2p" else "NCCL int32 reduce-scatter + fp16 all-gather")
     if getattr(wk, "p2p", None) is not None:
-        st = wk.p2p.status()
+        st = int(_max_over_ranks(float(wk.p2p.status()), world))  # same verdict on every rank
         torch.cuda.synchronize()
         import torch.distributed as dist
         dist.barrier()  # no rank unmaps its buffer while a peer may still read it
         wk.p2p.destroy()
         if st != 0:
-            raise RuntimeError("a bounded wait on a peer expired (status %d)" % st)
+            raise StatusWordSet("a bounded wait on a peer expired (status %d)" % st)
     if getattr(wk, "comm", None) is not None:
         torch.cuda.synchronize()
         pplb200.nccl_comm_destroy(wk.comm)
@@ -732,7 +737,11 @@ def main():
         for name in extra_names:
             if name == args.workload:
                 continue
-            ex = run_config(name, args, rank, world, "ours", True, False)
+            try:
+                ex = run_config(name, args, rank, world, "ours", True, False)
+            except StatusWordSet as e:  # raised on every rank alike: the headline line survives
+                extras[name] = {"error": str(e)}
+                continue
             extras[name] = {k: ex[k] for k in ("value", "unit", "ms_per_step", "scaling", "config", "e2e") if k in ex}
             if "roofline" in ex:
                 extras[name]["roofline"] = ex["roofline"]
