@@ -2,27 +2,30 @@
 """W8A8 (i8i8) linear benchmark: quantize + int8 GEMM + dequant(+bias)(+re-quantize).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c0..c4]
-                    [--extras]
+                    [--only] [--aux]
 
 One "step" = one pass of the whole path over one batch of synthetic input of the chosen
 configuration.  Prints ONE JSON line on rank 0.  metric = TOPS = 2*M*N*K / t.
+
+Headline workload: c4 (M 8192, K 8192, N 28672), the largest configuration that fits one GPU; on N > 1
+GPUs its N dimension is split over the ranks (column parallel, no communication, "scaling": "strong").
+The other configurations are measured in the same run and summarised under roofline.per_config
+(c0 / c1 / c2 / c3 on one GPU; c2 column-parallel and c3 row-parallel on N > 1 GPUs), so that one line
+carries all five.  --only skips them.
 
   value     device-resident: inputs already in HBM, CUDA-event time over K steps (max over ranks)
   e2e       same path with the step's activations copied from pinned host memory and the step's
             outputs copied back to pinned host memory inside the timed region (weights stay
             resident in HBM, as they do in the reference's deployment)
-  roofline  dominant kernel (the tcgen05 GEMM with fused epilogue) timed alone with CUDA events
+  roofline  dominant kernel (the tcgen05 GEMM with fused epilogue) timed alone with CUDA events;
+            peak = the int8 tensor-core ceiling measured in this run by the library's issue-rate probe
+            (prefill) or the measured copy bandwidth (decode)
   cpu_baseline  the scalar host oracle on the box's cores (a reported baseline, not a target)
 
 --impl reference runs the reference's own kernels (compiled unmodified into oracle/_ref:
-minmax_quantize_fp16 -> cuBLASLt gemm_i8i8i32 -> minmax_dequantize_fp16 [-> minmax_quantize_fp16])
-for the same workload; if that library is absent it times the host oracle port instead.
-
-Multi-GPU (torchrun, one rank per GPU): the default workload c1 does not shard ("replicas only",
-weak scaling: every rank runs its own batch).  With --workload c2/c4 the N dimension is split
-(column parallel, no communication), with --workload c3 the K dimension is split and the int32
-partial accumulators are all-reduced before the dequant epilogue (row parallel); these report
-"scaling": "strong".  --extras appends those sharded configurations to the default line.
+minmax_quantize_fp16 -> column_parallel_linear / row_parallel_linear with cuBLASLt int8 inside
+[-> minmax_quantize_fp16]) for the same workloads on the same number of GPUs; it never loads this
+repository's library.  If oracle/_ref is absent it times the host oracle port instead.
 """
 import argparse
 import ctypes
@@ -38,10 +41,14 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "ppl.llm.kernel.cuda_b200"))
 
 L2_BYTES_FALLBACK = 126 * 1024 * 1024
-
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (bytes).
-TRAFFIC_NCU = {"c1": 50973952 + 129792, "c2": 107780608 + 138983424}
+HEADLINE = "c4"
+ALL_CONFIGS = ("c0", "c1", "c2", "c3", "c4")
+METRIC = "W8A8 linear TOPS (quant+GEMM+dequant)"
+DTYPE = "int8 (int32 accumulate, fp16 in/out)"
+INT8_DATASHEET_TOPS = 4500.0
+HBM_DATASHEET_GBS = 8000.0
+# measured on this pool: SM stores of whole 128-byte lines into a peer's memory (GB/s per direction)
+PEER_STORE_GBS = 680.0
 
 
 def _peaks():
@@ -52,6 +59,17 @@ def _peaks():
         return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained"),
                     source="measured")
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def _ncu_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of each configuration's dominant kernel, from the
+    ncu captures summarised under profiles/ (bytes)."""
+    p = os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")
+    try:
+        with open(p) as f:
+            return json.load(f)["per_launch_bytes"]
+    except (OSError, KeyError, ValueError):
+        return {}
 
 
 class ClockSampler:
@@ -122,14 +140,18 @@ def _barrier(world):
     torch.cuda.synchronize()
 
 
-def _max_over_ranks(ms, world):
+def _reduce_over_ranks(v, world, op="max"):
     import torch
     if world == 1:
-        return ms
+        return v
     import torch.distributed as dist
-    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    t = torch.tensor([v], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.MIN)
     return float(t.item())
+
+
+def _max_over_ranks(ms, world):
+    return _reduce_over_ranks(ms, world, "max")
 
 
 def _time_steps(runner, steps, warmup, world):
@@ -222,13 +244,13 @@ class _Eager:
 
 class Workload:
     """Device-resident inputs of one configuration (one rank's shard), rotated over `nsets` distinct
-    copies so that consecutive steps do not hit each other's data in L2."""
+    copies so that consecutive steps do not hit each other's data in L2.  Uses torch and numpy only
+    (both arms of the benchmark build their inputs here)."""
 
-    def __init__(self, name, rank, world, sharded):
+    def __init__(self, name, rank, world, sharded, keep_full=False):
         import numpy as np
         import torch
-        import pplb200
-        from pplb200 import workloads as wl
+        import w8a8_workloads as wl
         self.name, self.cfg = name, wl.CONFIGS[name]
         c = self.cfg
         self.M, self.K, self.N = c["M"], c["K"], c["N"]
@@ -238,12 +260,20 @@ class Workload:
         w = wl.make_weights(name)
         sn = wl.make_column_scales(name)
         bias = wl.make_bias(name)
-        self.Kw, self.Nw = self.K, self.N
+        # the unsharded operands, for the sharded-equals-unsharded check (a seeded sample of rows)
+        self.full = None
+        if keep_full and self.shard is not None:
+            rows = np.unique(np.concatenate([np.arange(0, 128), np.arange(self.M - 128, self.M),
+                                             np.random.default_rng(7).integers(0, self.M, 256)]))
+            self.full = dict(rows=torch.from_numpy(rows).cuda(), x=torch.from_numpy(x[rows]).cuda(),
+                             w=torch.from_numpy(w).cuda(), sn=torch.from_numpy(sn).cuda(),
+                             bias=None if bias is None else torch.from_numpy(bias).cuda())
+        self.Kw, self.Nw, self.n0 = self.K, self.N, 0
         if self.shard == "column":
             n0, n1 = wl.shard_rows(self.N, world, rank)
             w, sn = w[n0:n1], sn[n0:n1]
             bias = None if bias is None else bias[n0:n1]
-            self.Nw = n1 - n0
+            self.Nw, self.n0 = n1 - n0, n0
         elif self.shard == "row":
             k0, k1 = wl.shard_rows(self.K, world, rank)
             w = np.ascontiguousarray(w[:, k0:k1])
@@ -264,9 +294,14 @@ class Workload:
                        ("one set of %.0f MB per step > L2 %.0f MB" % (bytes_per_set / 1e6, l2 / 1e6))
         self.ops = 2 * self.M * self.N * self.K  # whole-job ops of one step of the unsharded problem
 
+    def sharding_note(self):
+        if self.shard is None:
+            return "none"
+        return "%s-parallel over %d GPUs" % (self.shard, self.world)
+
 
 def build_ours(wk):
-    """Returns (step(i), e2e_step(i), kernel_only(i), launches_per_step, h2d, d2h, gemm_bytes)."""
+    """Returns (step(i), e2e_step(i), kernel_only(i), launches_per_step, h2d, d2h, gemm_bytes, result(s))."""
     import torch
     import pplb200
     M, K, N, Kw, Nw = wk.M, wk.K, wk.N, wk.Kw, wk.Nw
@@ -307,7 +342,7 @@ def build_ours(wk):
 
         gemm_bytes = M * K + Nw * K + 2 * Nw + (2 * Nw if wk.bias is not None else 0) + 2 * M + 2 * M * Nw
         launches = 2 + (1 if requant else 0)
-        return step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes
+        return step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes, (lambda s: lins[s].y)
 
     # row parallel: quantize the full activation rows (full-K absmax), GEMM on this rank's K shard,
     # exact int32 reduction, dequant epilogue.  Default: the reduction over peer-mapped memory (GEMM
@@ -371,7 +406,7 @@ def build_ours(wk):
             y_host.copy_(y, non_blocking=True)
 
         h2d = xs_host.numel() * 2
-        # the step's parts, timed one by one with --row-pieces (phases = 1 runs the GEMM and its pushes only)
+        # the step's parts, timed one by one (phases = 1 runs the GEMM and its pushes only)
         wk.pieces = {
             "sharded_quantizer": lambda i: pplb200.minmax_quantize_fp16_p2p(wk.p2p, xs[i % wk.nsets], out=xq_shard, scale=sm),
             "gemm_with_push": lambda i: pplb200.row_parallel_linear_p2p(wk.p2p, xq_shard, wk.w[i % wk.nsets], sm, wk.sn,
@@ -405,7 +440,7 @@ def build_ours(wk):
 
     gemm_bytes = M * Kw + N * Kw + 4 * M * N
     launches = 6 if wk.row_reduce == "p2p" else 3  # quantizer, GEMM, 2 flag kernels, reduce + dequant, row fetch
-    return step, e2e, kernel_only, launches, h2d, M * N * 2, gemm_bytes
+    return step, e2e, kernel_only, launches, h2d, M * N * 2, gemm_bytes, (lambda s: y)
 
 
 class RefLib:
@@ -419,14 +454,20 @@ class RefLib:
         self.lib.ref_minmax_dequantize_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, f32, f32, i32, vp]
         self.lib.ref_gemm_i8i8i32.argtypes = [vp, vp, vp, i64, i64, i64, vp, i64, vp]
         self.lib.ref_column_parallel_linear.argtypes = [vp, vp, vp, vp, vp, vp, f32, f32, i64, i64, i64, i32, vp, vp, i64, vp]
+        self.lib.ref_row_parallel_linear.argtypes = [vp, vp, vp, vp, vp, vp, f32, f32, i64, i64, i64, i32, i32, vp, vp, vp, i64, vp]
+        self.lib.ref_nccl_get_unique_id.argtypes = [vp]
+        self.lib.ref_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
+        self.lib.ref_nccl_comm_destroy.argtypes = [vp]
 
 
 def build_reference(wk):
-    """Reference arm: minmax_quantize_fp16 -> column_parallel_linear(gather_output=true, size 1)
-    [-> minmax_quantize_fp16 of the output], all the reference's own code."""
+    """Reference arm, all the reference's own code: minmax_quantize_fp16 -> column_parallel_linear
+    (gather_output = true on this rank's shard; cuBLASLt int8 inside) [-> minmax_quantize_fp16 of the
+    output]; for the row-parallel workload every rank quantizes its own K shard and calls the reference's
+    row_parallel_linear (dequantize, then fp16 all-reduce over NCCL)."""
     import torch
     ref = RefLib().lib
-    M, K, N = wk.M, wk.K, wk.Nw
+    M, K, N = wk.M, wk.Kw, wk.Nw
     requant = wk.cfg["requant"]
     dev = "cuda"
     xq = torch.empty((M, K), dtype=torch.int8, device=dev)
@@ -438,11 +479,31 @@ def build_reference(wk):
     ws = torch.empty((64 << 20,), dtype=torch.uint8, device=dev)
     P = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())
     S = lambda: ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    row = wk.shard == "row"
+    comm = ctypes.c_void_p()
+    if row:
+        import torch.distributed as dist
+        buf = ctypes.create_string_buffer(128)
+        if wk.rank == 0 and ref.ref_nccl_get_unique_id(buf):
+            raise RuntimeError("ncclGetUniqueId failed")
+        uid = [bytes(buf.raw) if wk.rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        if ref.ref_nccl_comm_init(ctypes.create_string_buffer(uid[0], 128), wk.rank, wk.world, ctypes.byref(comm)):
+            raise RuntimeError("ncclCommInitRank failed")
+        wk.ref_comm = (ref, comm)
+        xs = [wk.x[s][:, wk.k0:wk.k1].contiguous() for s in range(wk.nsets)]
+        xs_host = wk.x_host[:, wk.k0:wk.k1].contiguous().pin_memory()
+    else:
+        xs, xs_host = wk.x, wk.x_host
 
     def run(x, s):
         rc = ref.ref_minmax_quantize_fp16(S(), P(x), M, K, 4096.0, 0, P(xq), P(sm))
-        rc |= ref.ref_column_parallel_linear(S(), P(xq), P(wk.w[s]), P(wk.bias), P(sm), P(wk.sn), 1.0 / 4096, 1.0 / 8192,
-                                             M, N, K, 1, P(acc), P(ws), ws.numel(), P(ys[s]))
+        if row:
+            rc |= ref.ref_row_parallel_linear(S(), P(xq), P(wk.w[s]), P(wk.bias), P(sm), P(wk.sn), 1.0 / 4096, 1.0 / 8192,
+                                              M, N, wk.K, wk.rank, wk.world, comm, P(acc), P(ws), ws.numel(), P(ys[s]))
+        else:
+            rc |= ref.ref_column_parallel_linear(S(), P(xq), P(wk.w[s]), P(wk.bias), P(sm), P(wk.sn), 1.0 / 4096, 1.0 / 8192,
+                                                 M, N, K, 1, P(acc), P(ws), ws.numel(), P(ys[s]))
         if requant:
             rc |= ref.ref_minmax_quantize_fp16(S(), P(ys[s]), M, N, 4096.0, 0, P(yq), P(yqs))
         if rc:
@@ -450,25 +511,32 @@ def build_reference(wk):
 
     def step(i):
         s = i % wk.nsets
-        run(wk.x[s], s)
+        run(xs[s], s)
 
-    x_stage = torch.empty_like(wk.x[0])
+    x_stage = torch.empty_like(xs[0])
     y_host = torch.empty((M, N), dtype=torch.float16).pin_memory()
     yq_host = torch.empty((M, N), dtype=torch.int8).pin_memory() if requant else None
     ys_host = torch.empty((M,), dtype=torch.float16).pin_memory() if requant else None
 
     def e2e(i):
         s = i % wk.nsets
-        x_stage.copy_(wk.x_host, non_blocking=True)
+        x_stage.copy_(xs_host, non_blocking=True)
         run(x_stage, s)
         y_host.copy_(ys[s], non_blocking=True)
         if requant:
             yq_host.copy_(yq, non_blocking=True)
             ys_host.copy_(yqs, non_blocking=True)
 
-    h2d = wk.x_host.numel() * 2
+    # the reference's GEMM alone (cuBLASLt int8 through its gemm_i8i8i32 wrapper), on real operand values
+    def kernel_only(i):
+        s = i % wk.nsets
+        if ref.ref_gemm_i8i8i32(S(), P(xq), P(wk.w[s]), M, N, K, P(ws), ws.numel(), P(acc)):
+            raise RuntimeError("reference GEMM failed")
+
+    h2d = xs_host.numel() * 2
     d2h = M * N * 2 + ((M * N + M * 2) if requant else 0)
-    return step, e2e, None, 3 + (1 if requant else 0), h2d, d2h, None
+    gemm_bytes = M * K + N * K + 4 * M * N
+    return step, e2e, kernel_only, 3 + (1 if requant else 0), h2d, d2h, gemm_bytes, (lambda s: ys[s])
 
 
 def cpu_baseline(name, budget_s=12.0):
@@ -477,7 +545,7 @@ def cpu_baseline(name, budget_s=12.0):
     have been spent.  Returns the cpu_baseline object (TOPS from the fastest repetition)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as orc
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     c = wl.CONFIGS[name]
     cores = os.cpu_count() or 1
     orc.set_threads(cores)
@@ -502,132 +570,185 @@ def cpu_baseline(name, budget_s=12.0):
         best, spent, reps = min(best, dt), spent + dt, reps + 1
     tops = 2.0 * rows * c["N"] * c["K"] / best / 1e12
     return {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
-            "sample": "%d of %d token rows, full N=%d K=%d, %d repetitions, %.1f s of CPU work, best %.3f s"
-                      % (rows, c["M"], c["N"], c["K"], reps, spent, best)}
+            "sample": "%s: %d of %d token rows, full N=%d K=%d, %d repetitions, %.1f s of CPU work, best %.3f s"
+                      % (name, rows, c["M"], c["N"], c["K"], reps, spent, best)}
 
 
-def run_config(name, args, rank, world, impl, sharded, want_cpu):
+def _sharded_equals_unsharded(wk, result_of):
+    """Seeded sample of output rows of the sharded step against the unsharded fused linear run on this rank
+    with the full operands: 1.0 when bit-identical on every rank, else 0.0 (minimum over ranks)."""
     import torch
     import pplb200
-    from pplb200 import workloads as wl
-    peaks = _peaks()
-    wk = Workload(name, rank, world, sharded)
-    wk.row_reduce_wanted = args.row_reduce
-    if impl == "ours":
-        step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes = build_ours(wk)
-    else:
-        step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes = build_reference(wk)
+    f = wk.full
+    lin = pplb200.W8A8Linear(f["w"], f["sn"], f["bias"], max_tokens=f["x"].shape[0], requant=False)
+    y_full = lin(f["x"])
+    y = result_of(0).index_select(0, f["rows"])
+    if wk.shard == "column":
+        y_full = y_full[:, wk.n0:wk.n0 + wk.Nw]
+    torch.cuda.synchronize()
+    same = 1.0 if torch.equal(y.view(torch.int16), y_full.contiguous().view(torch.int16)) else 0.0
+    del lin, y_full
+    return _reduce_over_ranks(same, wk.world, "min")
 
-    sampler = ClockSampler(torch.cuda.current_device())
-    if rank == 0:
-        sampler.start()
+
+def run_config(name, args, rank, world, impl, sharded, sample_clocks=False, check_shard=False):
+    """Measures one configuration; returns a dict of raw results (identical on every rank where it matters)."""
+    import torch
+    wk = Workload(name, rank, world, sharded, keep_full=check_shard and impl == "ours")
+    wk.row_reduce_wanted = args.row_reduce
+    build = build_ours if impl == "ours" else build_reference
+    step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes, result_of = build(wk)
+
     # Eager passes first (one-time set-up, the reference's autotuner), then one CUDA graph per
-    # buffer set so that the host's launch cost does not bound these microsecond-scale steps.
-    # The row-parallel step contains NCCL collectives on a side stream; it is launched eagerly.
+    # buffer set so that the host's launch cost does not bound microsecond-scale steps.
+    # The row-parallel step exchanges data between ranks inside its kernels; it is launched eagerly.
     use_graphs = wk.shard != "row" and not args.no_graphs
     for s in range(wk.nsets):
         step(s)
         e2e(s)
-        if kernel_only:
-            kernel_only(s)
+        kernel_only(s)
     torch.cuda.synchronize()
+    bit_exact = None
+    if wk.full is not None:
+        step(0)
+        bit_exact = _sharded_equals_unsharded(wk, result_of) == 1.0
+        wk.full = None
     wrap = (lambda f: _Captured(f, wk.nsets)) if use_graphs else _Eager
-    step, e2e = wrap(step), wrap(e2e)
-    if kernel_only:
-        kernel_only = wrap(kernel_only)
+    step, e2e, kernel_only = wrap(step), wrap(e2e), wrap(kernel_only)
+    sampler = ClockSampler(torch.cuda.current_device()) if (sample_clocks and rank == 0) else None
+    if sampler:
+        sampler.start()
     ms = _time_steps(step, args.steps, args.warmup, world)
     ms_e2e = _time_steps(e2e, args.steps, args.warmup, world)
-    ms_k = _time_steps(kernel_only, args.steps, args.warmup, 1) if kernel_only else None
+    clocks = sampler.stop() if sampler else None
+    ms_k = _time_steps(kernel_only, args.steps, args.warmup, 1)
     reps = max(5, min(20, args.steps // max(1, wk.nsets)))
     med_ms, min_ms = _round_stats(step, wk.nsets, reps, world)
     warm_ms = None
     if use_graphs and wk.nsets > 1 and wk.cfg["bound"] == "hbm":
         warm_ms = _time_steps(_SameSet(step), args.steps, args.warmup, world) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    pieces = None
+    if getattr(wk, "pieces", None):
+        pieces = {k + "_us": _time_steps(_Eager(fn), args.steps, args.warmup, world) / args.steps * 1e3
+                  for k, fn in wk.pieces.items()}
+        wk.pieces = None
+
+    status_error = None
     if impl == "ours":
+        import pplb200
         st = int(_max_over_ranks(float(pplb200.gemm_status()), world))  # same verdict on every rank
         if st != 0:
-            raise StatusWordSet("GEMM kernel reported a timed-out wait (status %d)" % st)
-
-    replicas = world if (wk.shard is None and world > 1) else 1
-    ops_per_step = wk.ops * replicas
-    per_step = ms / args.steps
-    line = {
-        "metric": "W8A8 linear TOPS (quant+GEMM+dequant)",
-        "value": ops_per_step / (per_step * 1e-3) / 1e12,
-        "unit": "TOPS",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": per_step,
-        "higher_is_better": True,
-        "scaling": "weak" if wk.shard is None else "strong",
-        "vs_baseline": None,
-        "dtype": "int8 (int32 accumulate, fp16 in/out)",
-        "data": "synthetic",
-        "config": {
-            "workload": "%s: %s" % (name, wk.cfg["desc"]),
-            "M": wk.M, "K": wk.K, "N": wk.N,
-            "sharding": ("replicas only (x%d)" % world) if wk.shard is None and world > 1 else
-                        ("none" if wk.shard is None else "%s-parallel over %d GPUs" % (wk.shard, world)),
-            "l2": wk.l2_note,
-            "launch": ("CUDA graph replay, %d steps (one per buffer set) per graph" % wk.nsets) if use_graphs else "eager launches",
-            "ms_per_step_median": med_ms, "ms_per_step_min": min_ms,
-            "ms_per_step_stat": "over %d separately timed rounds of %d step(s)" % (reps, wk.nsets),
-            "l2_warm_ms_per_step": warm_ms,  # one buffer set replayed: operands served from L2, NOT the headline
-            "algorithmic_bytes_per_step": wl.algorithmic_bytes(name),
-            "gb_per_s": wl.algorithmic_bytes(name) * replicas / (per_step * 1e-3) / 1e9 if wk.shard is None else None,
-        },
-        "e2e": {"value": ops_per_step / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TOPS",
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "note": "activations in / outputs out through pinned host memory each step; weights resident"},
-        "gpu_launches": launches * args.steps,
-        "clocks": clocks,
-    }
-    if impl == "reference":
-        line["impl"] = "reference"
-        line["cpu_baseline"] = {"value": line["value"], "unit": "TOPS", "cores": 0, "kind": "reference",
-                                "sample": "full workload; the reference path is CUDA-only, so its own kernels "
-                                          "(compute_80 PTX JIT + cuBLASLt int8) run on the same GPU"}
-    if args.row_pieces and getattr(wk, "pieces", None):
-        pieces = {}
-        for name_, fn_ in wk.pieces.items():
-            pieces[name_ + "_us"] = _time_steps(_Eager(fn_), args.steps, args.warmup, world) / args.steps * 1e3
-        if ms_k is not None:
-            pieces["gemm_local_us"] = ms_k / args.steps * 1e3
-        line["row_parallel_pieces"] = pieces
-    if ms_k is not None and rank == 0:
-        kt = ms_k / args.steps * 1e-3
-        if wk.cfg["bound"] == "hbm":
-            ach = gemm_bytes / kt / 1e9
-            line["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                                "frac": ach / peaks["hbm_gbs"], "traffic": TRAFFIC_NCU.get(name), "kernel": "gemm_i8_decode_kernel",
-                                "kernel_us": kt * 1e6, "algorithmic_bytes_per_launch": gemm_bytes,
-                                "peak_source": "%s STREAM-copy GB/s" % peaks["source"],
-                                "frac_of_8TBs_datasheet": ach / 8000.0}
-        else:
-            ach = 2.0 * wk.M * wk.Nw * wk.Kw / kt / 1e12
-            peak = 2.0 * peaks["bf16_tflops"]
-            line["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TOP/s",
-                                "frac": ach / peak, "traffic": TRAFFIC_NCU.get(name), "kernel": "gemm_i8_tcgen05_pair_kernel",
-                                "kernel_us": kt * 1e6,
-                                "peak_source": "2 x %s cuBLAS bf16 burst TFLOP/s (int8 issues at twice the bf16 rate)" % peaks["source"],
-                                "frac_of_4500_datasheet": ach / 4500.0}
-    if want_cpu and rank == 0 and impl == "ours":
-        line["cpu_baseline"] = cpu_baseline(name)
-    if getattr(wk, "row_reduce", None) is not None:
-        line["config"]["row_reduce"] = ("activations quantized shard by shard (row maxima exchanged in the kernel), int32 tiles pushed to the row owner over peer-mapped memory, fp16 rows fetched back"
-                                        if wk.row_reduce == "p2p" else "NCCL int32 reduce-scatter + fp16 all-gather")
+            status_error = "GEMM kernel reported a timed-out wait (status %d)" % st
+    row_reduce = getattr(wk, "row_reduce", None)
     if getattr(wk, "p2p", None) is not None:
-        st = int(_max_over_ranks(float(wk.p2p.status()), world))  # same verdict on every rank
+        st = int(_max_over_ranks(float(wk.p2p.status()), world))
         torch.cuda.synchronize()
         import torch.distributed as dist
         dist.barrier()  # no rank unmaps its buffer while a peer may still read it
         wk.p2p.destroy()
+        wk.p2p = None
         if st != 0:
-            raise StatusWordSet("a bounded wait on a peer expired (status %d)" % st)
+            status_error = "a bounded wait on a peer expired (status %d)" % st
     if getattr(wk, "comm", None) is not None:
+        import pplb200
         torch.cuda.synchronize()
         pplb200.nccl_comm_destroy(wk.comm)
-    return line
+        wk.comm = None
+    if getattr(wk, "ref_comm", None) is not None:
+        torch.cuda.synchronize()
+        wk.ref_comm[0].ref_nccl_comm_destroy(wk.ref_comm[1])
+        wk.ref_comm = None
+    if status_error:
+        raise StatusWordSet(status_error)
+
+    # keep only plain numbers and strings: the device buffers are released when this function returns
+    import w8a8_workloads as wl
+    replicas = world if (wk.shard is None and world > 1) else 1
+    return dict(name=name, desc=wk.cfg["desc"], bound=wk.cfg["bound"], M=wk.M, K=wk.K, N=wk.N, Kw=wk.Kw, Nw=wk.Nw,
+                shard=wk.shard, world=world, replicas=replicas, ops=wk.ops, nsets=wk.nsets, l2_note=wk.l2_note,
+                sharding=("replicas only (x%d)" % world) if replicas > 1 else wk.sharding_note(),
+                alg_bytes=wl.algorithmic_bytes(name),
+                ms=ms, ms_e2e=ms_e2e, ms_k=ms_k, med_ms=med_ms, min_ms=min_ms, warm_ms=warm_ms,
+                launches=launches, h2d=h2d, d2h=d2h, gemm_bytes=gemm_bytes, clocks=clocks, use_graphs=use_graphs,
+                pieces=pieces, row_reduce=row_reduce, bit_exact=bit_exact, reps=reps)
+
+
+def static_config(res, others):
+    """The part of the line that names the workload: no measured value, identical for both arms."""
+    return {
+        "workload": "%s: %s" % (res["name"], res["desc"]),
+        "M": res["M"], "K": res["K"], "N": res["N"],
+        "sharding": res["sharding"],
+        "l2": res["l2_note"],
+        "algorithmic_bytes_per_step": res["alg_bytes"],
+        "inputs": "seeded synthetic tensors of the configuration's shapes and distributions (w8a8_workloads.py)",
+        "also_measured": list(others),
+    }
+
+
+def kernel_roofline(res, args, peaks, tensor_peak, impl):
+    """roofline-shaped object for the dominant kernel of one configuration."""
+    kt = res["ms_k"] / args.steps * 1e-3
+    traffic = _ncu_traffic().get(res["name"]) if (impl == "ours" and res["shard"] is None) else None
+    ref_kernel = "cuBLASLt int8 via the reference's gemm_i8i8i32"
+    if res["bound"] == "hbm":
+        ach = res["gemm_bytes"] / kt / 1e9
+        return {"bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                "traffic": traffic, "kernel": "gemm_i8_decode_kernel" if impl == "ours" else ref_kernel,
+                "kernel_us": kt * 1e6, "algorithmic_bytes_per_launch": res["gemm_bytes"],
+                "peak_source": "%s STREAM-copy GB/s" % peaks["source"], "frac_of_8TBs_datasheet": ach / HBM_DATASHEET_GBS}
+    ach = 2.0 * res["M"] * res["Nw"] * res["Kw"] / kt / 1e12
+    if tensor_peak is not None:
+        peak, src = tensor_peak["tops"], "int8 tcgen05 issue-rate probe of this run (%s)" % tensor_peak["how"]
+    else:
+        peak, src = 2.0 * peaks["bf16_tflops"], "2 x %s cuBLAS bf16 burst TFLOP/s (no int8 probe in this arm)" % peaks["source"]
+    return {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TOP/s", "frac": ach / peak, "traffic": traffic,
+            "kernel": "gemm_i8_tcgen05_pair_kernel" if impl == "ours" else ref_kernel,
+            "kernel_us": kt * 1e6, "peak_source": src, "frac_of_4500_datasheet": ach / INT8_DATASHEET_TOPS,
+            "frac_of_2x_bf16_burst": ach / (2.0 * peaks["bf16_tflops"])}
+
+
+def compact(res, args, peaks, tensor_peak, impl):
+    """Per-configuration summary (a few numbers) for roofline.per_config."""
+    world = res["world"]
+    per_step = res["ms"] / args.steps
+    rf = kernel_roofline(res, args, peaks, tensor_peak, impl)
+    out = {"sharding": res["sharding"], "ms_per_step": round(per_step, 6),
+           "tops": round(res["ops"] * res["replicas"] / (per_step * 1e-3) / 1e12, 2),
+           "e2e_tops": round(res["ops"] * res["replicas"] / (res["ms_e2e"] / args.steps * 1e-3) / 1e12, 2),
+           "kernel_us": round(rf["kernel_us"], 2), "bound": rf["bound"], "frac": round(rf["frac"], 4)}
+    if rf["bound"] == "tensor":
+        out["frac_of_datasheet"] = round(rf["frac_of_4500_datasheet"], 4)
+    else:
+        out["frac_of_datasheet"] = round(rf["frac_of_8TBs_datasheet"], 4)
+        out["step_gb_per_s"] = round(res["alg_bytes"] * res["replicas"] / (per_step * 1e-3) / 1e9, 1)
+        if res["warm_ms"] is not None:
+            out["l2_warm_ms_per_step"] = round(res["warm_ms"], 6)  # one buffer set replayed: NOT the headline
+    if res["bit_exact"] is not None:
+        out["sharded_bit_exact"] = bool(res["bit_exact"])
+    if res["row_reduce"] is not None:
+        out["row_reduce"] = res["row_reduce"]
+    if res["pieces"]:
+        out["pieces_us"] = {k: round(v, 1) for k, v in res["pieces"].items()}
+        if res["shard"] == "row":
+            wire = (world - 1) / world * res["M"] * res["N"] * 4 / (PEER_STORE_GBS * 1e9) * 1e6
+            out["wire_bound_us"] = round(wire + res["pieces"].get("sharded_quantizer_us", 0.0), 1)
+            out["wire_bound_note"] = ("int32 partials leaving each GPU / %.0f GB/s measured peer-store rate + sharded quantizer"
+                                      % PEER_STORE_GBS)
+    return out
+
+
+def tensor_peak_probe():
+    """The library's int8 tcgen05 issue-rate probe: every SM issues back-to-back kind::i8 MMAs on operands that
+    stay in shared memory (no loads, no epilogue).  Returns {"tops", "how", ...} or None."""
+    import pplb200
+    if not hasattr(pplb200, "tensor_peak_probe"):
+        return None
+    try:
+        return pplb200.tensor_peak_probe()
+    except Exception as e:  # the probe is diagnostic: a failure must not cost the bench line
+        sys.stderr.write("tensor peak probe failed: %s\n" % e)
+        return None
 
 
 def aux_kernels(steps, warmup):
@@ -678,33 +799,42 @@ def aux_kernels(steps, warmup):
         ms = _time_steps(_Eager(fn), steps, warmup, 1)
         t = ms / steps * 1e-3
         out[name] = {"shape": [M, K, 2 * D], "us": t * 1e6, "tops": 2.0 * M * 2 * D * K / t / 1e12}
+    if hasattr(pplb200, "stream_read_probe"):
+        # single-launch read-only TMA stream of a weight matrix: what a launch of that size can reach
+        out["tma_stream_read"] = pplb200.stream_read_probe()
     return out
 
 
 def reference_on_cpu(args, name):
     """Fallback reference arm when oracle/_ref is absent: the host port of the path."""
     cb = cpu_baseline(name)
-    return {"metric": "W8A8 linear TOPS (quant+GEMM+dequant)", "value": cb["value"], "unit": "TOPS", "n_gpus": args.gpus,
+    return {"metric": METRIC, "value": cb["value"], "unit": "TOPS", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int8 (int32 accumulate, fp16 in/out)",
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE,
             "data": "synthetic", "impl": "reference", "config": {"workload": name}, "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def _free():
+    import gc
+    import torch
+    gc.collect()
+    torch.cuda.empty_cache()
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c1")
-    ap.add_argument("--extras", action="store_true", help="also run the other configurations (sharded where they shard)")
-    ap.add_argument("--aux", action="store_true", help="also time the quantizer and the RMSNorm+quantize producer alone")
+    ap.add_argument("--workload", default=HEADLINE, choices=list(ALL_CONFIGS))
+    ap.add_argument("--only", action="store_true", help="measure the chosen workload alone (no per_config summary of the others)")
+    ap.add_argument("--aux", action="store_true", help="also time the quantizer, the RMSNorm+quantize producer and the probes alone")
     ap.add_argument("--row-reduce", default="p2p", choices=["p2p", "nccl"],
                     help="reduction of the row-parallel linear: over peer-mapped memory (default) or NCCL collectives")
-    ap.add_argument("--row-pieces", action="store_true",
-                    help="row-parallel workload over peer memory: also time the sharded quantizer, the GEMM with its pushes and the whole linear")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-t1", action="store_true", help="N > 1: skip the unsharded runs that give the same-run 1-GPU times")
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -712,46 +842,89 @@ def main():
     import torch
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback for the product path")
-    if args.impl == "reference":
-        # the reference arm runs on rank 0 alone (no process group is needed); other ranks leave
-        if int(os.environ.get("RANK", "0")) != 0:
-            return
-        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-        have_ref = os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libref_i8i8.so"))
-        if not have_ref:
+    impl = args.impl
+    if impl == "reference" and not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "libref_i8i8.so")):
+        if int(os.environ.get("RANK", "0")) == 0:
             print(json.dumps(reference_on_cpu(args, args.workload)))
-            return
-        line = run_config(args.workload, args, 0, 1, "reference", False, False)
-        line["n_gpus"] = args.gpus
-        print(json.dumps(line))
         return
 
     rank, world = _dist_setup(args.gpus)
-    sharded = args.workload != "c1"
-    line = run_config(args.workload, args, rank, world, "ours", sharded, not args.no_cpu and world == 1)
-    # On more than one GPU the default line (c1 replicas) is accompanied by the two configurations
-    # that really shard: c2 (column parallel, no communication) and c3 (row parallel, int32 reduction).
-    extra_names = ("c0", "c1", "c2", "c3", "c4") if args.extras else (("c2", "c3") if world > 1 and not sharded else ())
-    if extra_names:
-        extras = {}
-        for name in extra_names:
-            if name == args.workload:
-                continue
-            try:
-                ex = run_config(name, args, rank, world, "ours", True, False)
-            except StatusWordSet as e:  # raised on every rank alike: the headline line survives
-                extras[name] = {"error": str(e)}
-                continue
-            extras[name] = {k: ex[k] for k in ("value", "unit", "ms_per_step", "scaling", "config", "e2e") if k in ex}
-            if "roofline" in ex:
-                extras[name]["roofline"] = ex["roofline"]
-        line["other_configs"] = extras
-    if args.aux and rank == 0:
+    peaks = _peaks()
+    tensor_peak = tensor_peak_probe() if impl == "ours" else None
+    import w8a8_workloads as wl
+    head = args.workload
+    if args.only:
+        others = []
+    elif world == 1:
+        others = [c for c in ALL_CONFIGS if c != head]
+    else:  # c0 / c1 are single-GPU configurations by definition
+        others = [c for c in ALL_CONFIGS if c != head and wl.CONFIGS[c]["shard"] is not None]
+
+    def summary_of(name):
+        """One configuration, sharded where it shards; on N > 1 GPUs also unsharded for the same-run 1-GPU time."""
+        r = run_config(name, args, rank, world, impl, True, sample_clocks=(name == head), check_shard=world > 1)
+        _free()
+        s = compact(r, args, peaks, tensor_peak, impl)
+        if r["shard"] is not None and impl == "ours" and not args.no_t1:
+            t1 = run_config(name, args, rank, world, impl, False)["ms"] / args.steps
+            _free()
+            s["ms_per_step_1gpu_same_run"] = round(t1, 6)
+            s["scaling_vs_1gpu"] = round(t1 / s["ms_per_step"], 3)
+        return r, s
+
+    res, head_summary = summary_of(head)
+    per_step = res["ms"] / args.steps
+    ops_per_step = res["ops"] * res["replicas"]
+    line = {
+        "metric": METRIC,
+        "value": ops_per_step / (per_step * 1e-3) / 1e12,
+        "unit": "TOPS",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_step,
+        "higher_is_better": True,
+        "scaling": "weak" if res["replicas"] > 1 else "strong",
+        "vs_baseline": None,
+        "dtype": DTYPE,
+        "data": "synthetic",
+        "config": static_config(res, others),
+        "e2e": {"value": ops_per_step / (res["ms_e2e"] / args.steps * 1e-3) / 1e12, "unit": "TOPS",
+                "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
+                "note": "activations in / outputs out through pinned host memory each step; weights resident"},
+        "gpu_launches": res["launches"] * args.steps,
+        "clocks": res["clocks"],
+    }
+    rf = kernel_roofline(res, args, peaks, tensor_peak, impl)
+    if res["bit_exact"] is not None:
+        rf["sharded_bit_exact"] = bool(res["bit_exact"])
+    stats = {"launch": ("CUDA graph replay, %d step(s) per graph" % res["nsets"]) if res["use_graphs"] else "eager launches",
+             "ms_per_step_median": res["med_ms"], "ms_per_step_min": res["min_ms"],
+             "ms_per_step_stat": "over %d separately timed rounds of %d step(s)" % (res["reps"], res["nsets"])}
+    if tensor_peak is not None:
+        stats["tensor_peak_probe"] = tensor_peak
+    per_config = {head: head_summary}
+    for name in others:
+        try:
+            per_config[name] = summary_of(name)[1]
+        except StatusWordSet as e:  # raised on every rank alike: the headline line survives
+            per_config[name] = {"error": str(e)}
+            _free()
+    rf["per_config"] = per_config
+    line["roofline"] = rf
+    line["stats"] = stats
+    if impl == "reference":
+        line["impl"] = "reference"
+        line["cpu_baseline"] = {"value": line["value"], "unit": "TOPS", "cores": 0, "kind": "reference",
+                                "sample": "full workload; the reference path is CUDA-only, so its own kernels "
+                                          "(compute_80 PTX JIT + cuBLASLt int8) run on the same GPUs, one rank per GPU"}
+    elif world == 1 and rank == 0 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline(head)
+    if args.aux and rank == 0 and impl == "ours":
         line["aux_kernels"] = aux_kernels(args.steps, args.warmup)
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
         import torch.distributed as dist
+        dist.barrier()
         dist.destroy_process_group()
 
 

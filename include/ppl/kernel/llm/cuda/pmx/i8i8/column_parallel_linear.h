@@ -18,7 +18,7 @@ namespace ppl { namespace kernel { namespace llm { namespace cuda { namespace pm
 //   gather_output == true  -> fp16 [M, N] (all-gathered over the communicator when size > 1)
 // cublasLt handle / algo / algo cache / cuBLAS workspace are accepted and ignored; quant_buffer
 // is not needed (the int32 accumulators stay in tensor memory) but accepted.
-inline ppl::common::RetCode column_parallel_linear(
+static inline ppl::common::RetCode column_parallel_linear(
     const cudaStream_t stream,
     const cublasLtHandle_t& cublaslt_handle,
     const cublasLtMatmulAlgo_t* algo,

@@ -17,7 +17,7 @@ constexpr float hidden_up_scale = 8192.0f;
 constexpr float token_down_scale = 1.0f / 4096.0f;
 constexpr float hidden_down_scale = 1.0f / 8192.0f;
 
-inline ppl::common::RetCode minmax_quantize_fp16(
+static inline ppl::common::RetCode minmax_quantize_fp16(
     cudaStream_t stream,
     const void* input,           // fp16, [batch, quant_dim]
     const int64_t batch,
@@ -31,7 +31,7 @@ inline ppl::common::RetCode minmax_quantize_fp16(
         (pplb200_stream_t)stream, input, batch, quant_dim, up_scale, (int32_t)to_layout, quantized, scale);
 }
 
-inline ppl::common::RetCode minmax_dequantize_fp16(
+static inline ppl::common::RetCode minmax_dequantize_fp16(
     cudaStream_t stream,
     const void* input,              // int32, [batch, quant_dim] in from_layout
     const void* optional_bias,      // fp16, [quant_dim]
@@ -50,7 +50,7 @@ inline ppl::common::RetCode minmax_dequantize_fp16(
 }
 
 // Consumers of the raw int32 GEMM output; reference declarations quantize.h:57-126.
-inline ppl::common::RetCode minmax_dequantize_split3_fp16(
+static inline ppl::common::RetCode minmax_dequantize_split3_fp16(
     cudaStream_t stream, const void* input, const void* optional_bias, const void* scale_per_batch,
     const void* scale_per_channel, const int64_t batch, const int64_t quant_dim, const int64_t split_dim_0,
     const int64_t split_dim_1, const int64_t split_dim_2, const float down_scale_batch, const float down_scale_channel,
@@ -61,7 +61,7 @@ inline ppl::common::RetCode minmax_dequantize_split3_fp16(
         split_dim_1, split_dim_2, down_scale_batch, down_scale_channel, (int32_t)from_layout, output_0, output_1, output_2);
 }
 
-inline ppl::common::RetCode minmax_dequantize_silu_fp16(
+static inline ppl::common::RetCode minmax_dequantize_silu_fp16(
     cudaStream_t stream, const void* input, const void* input_scale_per_batch, const void* input_scale_per_channel,
     const void* optional_gate, const void* gate_scale_per_batch, const void* gate_scale_per_channel, const int64_t batch,
     const int64_t quant_dim, const matrix_layout_t from_layout, float down_scale_batch, float down_scale_channel,
@@ -72,7 +72,7 @@ inline ppl::common::RetCode minmax_dequantize_silu_fp16(
         gate_scale_per_channel, batch, quant_dim, (int32_t)from_layout, down_scale_batch, down_scale_channel, output);
 }
 
-inline ppl::common::RetCode minmax_requantize_silu_fp16(
+static inline ppl::common::RetCode minmax_requantize_silu_fp16(
     cudaStream_t stream, const void* input, const void* input_scale_per_batch, const void* input_scale_per_channel,
     const void* optional_gate, const void* gate_scale_per_batch, const void* gate_scale_per_channel, const int64_t batch,
     const int64_t quant_dim, const matrix_layout_t layout, const float up_scale, const float down_scale_batch,
@@ -84,7 +84,7 @@ inline ppl::common::RetCode minmax_requantize_silu_fp16(
         output, scale);
 }
 
-inline ppl::common::RetCode minmax_requantize_swiglu_fp16(
+static inline ppl::common::RetCode minmax_requantize_swiglu_fp16(
     cudaStream_t stream, const void* input, const void* input_scale_per_batch, const void* input_scale_per_channel,
     const int64_t batch, const int64_t quant_dim, const float beta, const matrix_layout_t layout, const float up_scale,
     const float down_scale_batch, const float down_scale_channel, void* workspace, void* output, void* scale)
@@ -96,7 +96,7 @@ inline ppl::common::RetCode minmax_requantize_swiglu_fp16(
 
 // input + skip -> skip_out; quantize(rmsnorm(input + skip) * weight) -> output, output_scale
 // (reference: include/ppl/kernel/llm/cuda/pmx/i8i8/quantize.h:128-141).
-inline ppl::common::RetCode skip_rmsnorm_minmax_quantize_fp16(
+static inline ppl::common::RetCode skip_rmsnorm_minmax_quantize_fp16(
     const cudaStream_t stream,
     const void* input,            // [batch, hidden dim]
     const void* weight,           // [hidden dim]

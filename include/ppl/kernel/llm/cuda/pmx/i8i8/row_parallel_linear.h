@@ -14,18 +14,21 @@
 namespace ppl { namespace kernel { namespace llm { namespace cuda { namespace pmx { namespace i8i8 {
 
 // How partial results of the K shards are combined when nccl_param->size > 1.
-//   ROW_PARALLEL_REDUCE_INT32 (default): sum the int32 accumulators across ranks, then run the
-//     dequant + bias epilogue once -- bit-identical to the unsharded linear.  Needs quant_buffer
-//     (int32 [M, N]); every rank passes the same full-row scale_M and the same bias.
-//   ROW_PARALLEL_REDUCE_FP16_REFERENCE: the reference's order -- dequantize each partial to fp16
-//     (bias on rank 0 only) and all-reduce in fp16 (src/.../pmx/i8i8/row_parallel_linear.cu:84,131-158).
+//   ROW_PARALLEL_REDUCE_FP16_REFERENCE (default of the overload with the reference's argument list): the
+//     reference's order -- dequantize each partial to fp16 with THIS rank's scale_M (bias on rank 0 only) and
+//     all-reduce in fp16 (src/.../pmx/i8i8/row_parallel_linear.cu:84,131-158).  This is what an unchanged
+//     caller expects: it quantizes each K shard on its own rank, so scale_M differs from rank to rank.
+//   ROW_PARALLEL_REDUCE_INT32 (opt-in): sum the int32 accumulators across ranks, then run the dequant + bias
+//     epilogue once -- bit-identical to the unsharded linear.  Only meaningful when every rank passes the SAME
+//     full-row scale_M (activations quantized with the maximum over the whole row, e.g. by
+//     minmax_quantize_fp16_sharded below) and the same bias; needs quant_buffer (int32 [M, N]).
 enum row_parallel_reduce_t {
     ROW_PARALLEL_REDUCE_INT32 = 0,
     ROW_PARALLEL_REDUCE_FP16_REFERENCE = 1,
 };
 
 // input int8 [.., K/size]; weight int8 [N, K/size] row-major; output fp16 [M, N] on every rank.
-inline ppl::common::RetCode row_parallel_linear(
+static inline ppl::common::RetCode row_parallel_linear(
     const cudaStream_t stream,
     const cublasLtHandle_t& cublaslt_handle,
     const cublasLtMatmulAlgo_t* algo,
@@ -51,7 +54,7 @@ inline ppl::common::RetCode row_parallel_linear(
     ppl::kernel::llm::cuda::cublas::AlgoCache* cublas_algo_cache,
     const ppl::common::TensorShape* output_shape,
     void* output,
-    const row_parallel_reduce_t reduce = ROW_PARALLEL_REDUCE_INT32)
+    const row_parallel_reduce_t reduce = ROW_PARALLEL_REDUCE_FP16_REFERENCE)
 {
     (void)cublaslt_handle; (void)algo; (void)weight_shape; (void)split_buffer; (void)cublas_algo_cache; (void)output_shape;
     if (bias && bias_shape->GetDataType() != ppl::common::DATATYPE_FLOAT16) {
@@ -71,7 +74,7 @@ inline ppl::common::RetCode row_parallel_linear(
 // connected to its peers; it replaces nccl_param, quant_buffer and the cuBLAS arguments.  Result
 // and argument meaning as ROW_PARALLEL_REDUCE_INT32; M must be divisible by the number of ranks
 // (RC_UNSUPPORTED otherwise: call the overload above).  No counterpart in the reference.
-inline ppl::common::RetCode row_parallel_linear(
+static inline ppl::common::RetCode row_parallel_linear(
     const cudaStream_t stream,
     void* p2p_context,
     const ppl::common::TensorShape* input_shape,
@@ -100,7 +103,7 @@ inline ppl::common::RetCode row_parallel_linear(
 // Per-token quantizer for activations sharded along the quantized dimension (what the preceding
 // column-parallel operator leaves on each rank): int8 values and full-row scales equal those of
 // minmax_quantize_fp16 on the unsharded rows.  input_shape is the shard's shape [.., K / size].
-inline ppl::common::RetCode minmax_quantize_fp16_sharded(
+static inline ppl::common::RetCode minmax_quantize_fp16_sharded(
     const cudaStream_t stream,
     void* p2p_context,
     const ppl::common::TensorShape* input_shape,

@@ -154,6 +154,17 @@ int32_t pplb200_i8i8_gemm(pplb200_stream_t stream, const void* A, int64_t lda, c
                           void* ws, int64_t ws_bytes, void* out, int64_t ldc, void* out_q, void* out_q_scale);
 
 /*
+ * C[M,N] (int32, ldc) = alpha * (A[M,K] x B[N,K]^T) + beta * C + optional_bias_i32[n], in wrapping int32
+ * arithmetic: the full contract of ppl::kernel::llm::cuda::cublas::gemm_i8i8i32 (int32 alpha / beta and the
+ * int32 bias epilogue; include/ppl/kernel/llm/cuda/cublas/gemm.h:56-79, src/.../cublas/gemm.cu:187-188,239-243,329-345).
+ * With alpha = 1, beta = 0 and no bias it is pplb200_i8i8_gemm in RAW_I32 mode.  beta != 0 reads C before it
+ * is overwritten.  Same shape and alignment rules as pplb200_i8i8_gemm; the bias pointer 16-byte aligned.
+ */
+int32_t pplb200_i8i8_gemm_i32(pplb200_stream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb,
+                              int64_t M, int64_t N, int64_t K, int32_t alpha, int32_t beta, const void* optional_bias_i32,
+                              void* C, int64_t ldc);
+
+/*
  * Same result as pplb200_i8i8_gemm with PPLB200_EPI_DEQUANT_F16_REQUANT_I8 (out fp16 [M,N] with
  * ldc == N, out_q int8 [M,N], out_q_scale fp16 [M]) but WITHOUT a workspace argument and without
  * allocating anything: the per-row scratch lives in a fixed array inside the library.
@@ -309,9 +320,23 @@ int32_t pplb200_nccl_comm_destroy(void* comm);
 /*
  * Device-side health word of the GEMM kernel: every bounded wait in the kernel that gives
  * up records a code here instead of hanging.  Returns 0 if no kernel launched on the current
- * device has timed out since the last call with reset != 0.  Synchronises the device.
+ * device has timed out since the last call with reset != 0.  Reads the word as it is now on a private
+ * stream (no other stream is waited for): synchronise the streams you launched on before asking about them.
  */
 int32_t pplb200_i8i8_gemm_status(int32_t reset);
+
+/*
+ * Measurement probes (no counterpart in the reference; they give the roofline denominators that
+ * bench.py reports against).  `result24` is a 24-byte device record the launch fills:
+ *   uint64 cycles, uint64 nanoseconds (of CTA 0, from first issue to completion), uint32 status, uint32 pad;
+ * status != 0 means a bounded wait inside the probe gave up.
+ * tensor_peak: every SM issues `mmas_per_cta` back-to-back tcgen05.mma kind::i8 (M 128 x N 256 x K 32 per CTA,
+ *   or M 256 x N 256 x K 32 per CTA pair when cta_pairs != 0) on operands resident in shared memory.
+ * stream_read: one launch reads `bytes` (a multiple of 32 KiB is used) from `src` with bulk asynchronous copies
+ *   and discards them.
+ */
+int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream, int32_t cta_pairs, int32_t mmas_per_cta, void* result24);
+int32_t pplb200_probe_stream_read(pplb200_stream_t stream, const void* src, int64_t bytes, void* result24);
 
 /*
  * Host-only helper: element offset of (row, col) in a [rows, cols] matrix stored in `layout`

@@ -10,6 +10,8 @@
 
 #include <cublasLt.h>
 #include <mutex>
+#include <nccl.h>
+#include <string.h>
 
 namespace refns = ppl::kernel::llm::cuda;
 
@@ -133,5 +135,51 @@ int32_t ref_row_parallel_linear(cudaStream_t stream, const void* xq, const void*
         refns::MATRIX_LAYOUT_ROW_MAJOR, &nccl, true, nullptr, quant_buffer, workspace_bytes, workspace,
         &s.cache, &o_shape, out);
 }
+
+// The reference's column_parallel_linear on one rank of `size` with gather_output = true: dequantized
+// shard -> gather_buffer -> all-gather -> [size, M, N/size] -> [M, N] transpose into `out`.
+int32_t ref_column_parallel_linear_tp(cudaStream_t stream, const void* xq, const void* w, const void* bias,
+                                      const void* sm, const void* sn, float down_m, float down_n,
+                                      int64_t M, int64_t N_total, int64_t K, int32_t rank, int32_t size, void* comm,
+                                      void* gather_buffer, void* quant_buffer, void* workspace, int64_t workspace_bytes,
+                                      void* out) {
+    RefState& s = state();
+    ppl::common::TensorShape in_shape(ppl::common::DATATYPE_INT8, {M, K});
+    ppl::common::TensorShape w_shape(ppl::common::DATATYPE_INT8, {N_total / size, K});
+    ppl::common::TensorShape b_shape(ppl::common::DATATYPE_FLOAT16, {N_total / size});
+    ppl::common::TensorShape o_shape(ppl::common::DATATYPE_FLOAT16, {M, N_total});
+    ppl::common::NcclParam nccl;
+    nccl.rank = rank; nccl.size = size; nccl.comm = (ncclComm_t)comm;
+    return (int32_t)refns::pmx::i8i8::column_parallel_linear(
+        stream, s.lt, nullptr, &in_shape, xq, &w_shape, w, &b_shape, bias, sm, sn, down_m, down_n, K, N_total,
+        refns::MATRIX_LAYOUT_ROW_MAJOR, &nccl, true, gather_buffer, quant_buffer, workspace_bytes, workspace,
+        &s.cache, &o_shape, out);
+}
+
+// The reference's GEMM on the Turing / Ampere operand orders (A, C in COL32; B in COL32_2R_4R4 or
+// COL4_4R2_8C).  Returns the reference's RetCode; *cublas_status_out receives nothing more than that
+// (the wrapper folds the cuBLASLt status into RC_DEVICE_RUNTIME_ERROR and logs it).
+int32_t ref_gemm_i8i8i32_col32(cudaStream_t stream, const void* input_col32, const void* kernel, int64_t M, int64_t N,
+                               int64_t K, int32_t use_4r4_kernel, void* output_col32) {
+    RefState& s = state();
+    return (int32_t)refns::cublas::gemm_i8i8i32_col32(stream, s.lt, input_col32, kernel, M, N, K, use_4r4_kernel != 0,
+                                                      output_col32);
+}
+
+// Communicator plumbing for the reference arm of the benchmark and the multi-GPU parity tests, so
+// that they need nothing but this library (same NCCL as the collectives above).
+int32_t ref_nccl_get_unique_id(void* id128_host) {
+    static_assert(sizeof(ncclUniqueId) == 128, "unique id size");
+    return ncclGetUniqueId((ncclUniqueId*)id128_host) == ncclSuccess ? 0 : 10;
+}
+int32_t ref_nccl_comm_init(const void* id128_host, int32_t rank, int32_t size, void** comm_out) {
+    ncclUniqueId id;
+    memcpy(&id, id128_host, sizeof(id));
+    ncclComm_t comm = nullptr;
+    if (ncclCommInitRank(&comm, size, id, rank) != ncclSuccess) return 10;
+    *comm_out = comm;
+    return 0;
+}
+int32_t ref_nccl_comm_destroy(void* comm) { return comm && ncclCommDestroy((ncclComm_t)comm) != ncclSuccess ? 10 : 0; }
 
 }

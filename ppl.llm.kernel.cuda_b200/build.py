@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libpplb200_i8i8.so")
-SOURCES = ["capi.cu", "quantize.cu", "rmsnorm_quantize.cu", "activation_requant.cu", "gemm_i8_tcgen05.cu", "gemm_i8_decode.cu", "tensor_parallel.cu", "p2p_row_parallel.cu", "no_alloc.cu"]
+SOURCES = ["capi.cu", "quantize.cu", "rmsnorm_quantize.cu", "activation_requant.cu", "gemm_i8_tcgen05.cu", "gemm_i8_decode.cu", "tensor_parallel.cu", "p2p_row_parallel.cu", "no_alloc.cu", "probes.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-std=c++17", "-O3", "-lineinfo",

@@ -262,6 +262,23 @@ int32_t pplb200_i8i8_gemm(pplb200_stream_t stream, const void* A, int64_t lda, c
                       down_scale_M, down_scale_N, requant_up_scale, ws, ws_bytes, out, ldc, out_q, out_q_scale, false);
 }
 
+int32_t pplb200_i8i8_gemm_i32(pplb200_stream_t stream, const void* A, int64_t lda, const void* B, int64_t ldb,
+                              int64_t M, int64_t N, int64_t K, int32_t alpha, int32_t beta, const void* optional_bias_i32,
+                              void* C, int64_t ldc) {
+    int32_t rc = check_gemm_args(A, lda, B, ldb, M, N, K, EPI_RAW_I32, nullptr, nullptr, nullptr, C, ldc, nullptr, nullptr);
+    if (rc != RC_SUCCESS || M == 0 || N == 0) return rc;
+    if (optional_bias_i32 && !aligned16(optional_bias_i32)) return fail(RC_INVALID_VALUE, "int32 bias must be 16-byte aligned");
+    GemmArgs g;
+    g.A = (const int8_t*)A; g.lda = lda; g.B = (const int8_t*)B; g.ldb = ldb;
+    g.M = M; g.N = N; g.K = K; g.mode = EPI_RAW_I32;
+    g.scale_m = nullptr; g.scale_n = nullptr; g.bias = nullptr;
+    g.down_m = 0.f; g.down_n = 0.f;
+    g.out = C; g.ldc = ldc;
+    g.row_absmax_bits = nullptr;
+    g.raw_alpha = alpha; g.raw_beta = beta; g.raw_bias = (const int32_t*)optional_bias_i32;
+    return launch_gemm((cudaStream_t)stream, g);
+}
+
 int64_t pplb200_i8i8_linear_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode) {
     (void)N;
     return round_up(M * K, WS_ALIGN) + round_up(M * 2, WS_ALIGN) + gemm_ws_bytes(M, epilogue_mode);

@@ -108,6 +108,10 @@ struct GemmArgs {
     uint32_t* row_absmax_bits; // mode 2: per-row max |y| as float bits, zeroed by the launcher
     bool pdl = false;          // launch as a programmatic dependent of the preceding kernel
     float beta = 1.0f;         // EPI_SWIGLU_F16
+    // EPI_RAW_I32 only: out = raw_alpha * acc + raw_beta * out + raw_bias[n] in wrapping int32 (the scaling and
+    // int32 bias of the reference's gemm_i8i8i32, src/ppl/kernel/llm/cuda/cublas/gemm.cu:187-188,239-243)
+    int32_t raw_alpha = 1, raw_beta = 0;
+    const int32_t* raw_bias = nullptr;
     // EPI_PUSH_I32: output row r belongs to rank r / push_rows; it is stored at
     // push_base[owner] + ((push_rank * push_rows + r % push_rows) * ldc + col) (int32 elements).
     int32_t* push_base[kMaxPeers] = {};

@@ -45,6 +45,9 @@ struct DecodeParams {
     float down_m, down_n;
     uint32_t* row_absmax_bits;
     unsigned int* status;
+    // EPI_RAW_I32 with raw_affine != 0: out = raw_alpha * acc + raw_beta * out + raw_bias[n] (wrapping int32)
+    int32_t raw_affine, raw_alpha, raw_beta;
+    const int32_t* raw_bias;
 };
 
 template <int BT> struct DCfg {
@@ -352,9 +355,17 @@ gemm_i8_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
                     const int m0 = c0 + s8 * 8;
                     if (mode == EPI_RAW_I32) {
                         int32_t* dst = reinterpret_cast<int32_t*>(p.out) + (int64_t)m0 * p.ldc + n;
+                        const uint32_t add = (p.raw_affine && p.raw_bias != nullptr && n_ok) ? (uint32_t)p.raw_bias[n] : 0u;
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
-                            if (n_ok && m0 + j < M) dst[(int64_t)j * p.ldc] = (int32_t)v[j];
+                            if (n_ok && m0 + j < M) {
+                                uint32_t r = v[j];
+                                if (p.raw_affine) {
+                                    r = (uint32_t)p.raw_alpha * r + add;
+                                    if (p.raw_beta != 0) r += (uint32_t)p.raw_beta * (uint32_t)dst[(int64_t)j * p.ldc];
+                                }
+                                dst[(int64_t)j * p.ldc] = (int32_t)r;
+                            }
                     } else {
                         // eight independent chains, no control flow between them
                         const float4 ts0 = *reinterpret_cast<const float4*>(&token_scale[m0]);
@@ -474,6 +485,8 @@ int32_t launch_bt(cudaStream_t stream, const GemmArgs& a, const DecDeviceInfo& d
     p.down_m = a.down_m; p.down_n = a.down_n;
     p.row_absmax_bits = a.row_absmax_bits;
     p.status = status;
+    p.raw_alpha = a.raw_alpha; p.raw_beta = a.raw_beta; p.raw_bias = a.raw_bias;
+    p.raw_affine = (a.raw_alpha != 1 || a.raw_beta != 0 || a.raw_bias != nullptr) ? 1 : 0;
 
     const int n_tiles = (int)((a.N + BW - 1) / BW);
     // K split: one CTA per SM is resident (the ring takes the whole shared memory), so split K only as

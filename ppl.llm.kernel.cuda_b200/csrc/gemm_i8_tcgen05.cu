@@ -17,6 +17,7 @@
 #include "ptx.cuh"
 
 #include <mutex>
+#include <string.h>
 
 namespace pplb200 {
 
@@ -45,6 +46,9 @@ struct KernelParams {
     float down_m, down_n;
     uint32_t* row_absmax_bits;
     unsigned int* status;
+    // EPI_RAW_I32 with raw_affine != 0: out = raw_alpha * acc + raw_beta * out + raw_bias[n] (wrapping int32)
+    int32_t raw_affine, raw_alpha, raw_beta;
+    const int32_t* raw_bias;
     // EPI_SWIGLU_F16 (CTA-pair kernel only): B = [x rows | gate rows], act_dim rows each
     int32_t act_dim;
     float beta;
@@ -57,45 +61,144 @@ template <int BN> struct Cfg {
     static constexpr int A_BYTES = BM * BK;
     static constexpr int B_BYTES = BN * BK;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    // the epilogue's staging buffers (EPI_STAGE_BYTES of static shared memory) come on top of the ring
     static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128) ? 6 : 8;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024; // + slack to align the ring to 1024 B
     static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
-    static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "UMMA N for M = 128");
+    static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "UMMA N for M = 128; the epilogue stores 64-column slabs");
     // More than half of the SM's shared memory: at most one CTA per SM, so two CTAs can never
     // compete for (and block on) the same SM's tensor memory.
     static_assert(SMEM_BYTES > 116 * 1024 && SMEM_BYTES <= 227 * 1024, "smem budget");
 };
 
 // Dequantize + optional bias for 8 consecutive columns; returns packed halves.
+template <bool ABSMAX>
 __device__ __forceinline__ uint4 dequant8(const uint32_t* acc, const half* sn8, const half* bias8, float down_n,
-                                          float batch_scale, bool has_bias, __half& running_absmax) {
+                                          float batch_scale, bool has_bias, __half2& running_absmax) {
     uint4 ov;
-    half* o = reinterpret_cast<half*>(&ov);
+    __half2* o = reinterpret_cast<__half2*>(&ov);
     const uint4 snv = *reinterpret_cast<const uint4*>(sn8);
-    const half* sn = reinterpret_cast<const half*>(&snv);
+    const __half2* sn = reinterpret_cast<const __half2*>(&snv);
     uint4 bv = make_uint4(0, 0, 0, 0);
     if (has_bias) bv = *reinterpret_cast<const uint4*>(bias8);
-    const half* b = reinterpret_cast<const half*>(&bv);
+    const __half2* b = reinterpret_cast<const __half2*>(&bv);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
+    for (int j = 0; j < 4; ++j) {
         // three separately rounded fp32 products in the reference's order, then fp16, then fp16 bias add
-        float t = __fmul_rn((float)(int32_t)acc[j], __half2float(sn[j]));
-        t = __fmul_rn(t, down_n);
-        t = __fmul_rn(t, batch_scale);
-        half h = __float2half_rn(t);
-        if (has_bias) h = __hadd(h, b[j]);
+        const float2 s2 = __half22float2(sn[j]);
+        float t0 = __fmul_rn((float)(int32_t)acc[2 * j], s2.x);
+        float t1 = __fmul_rn((float)(int32_t)acc[2 * j + 1], s2.y);
+        t0 = __fmul_rn(t0, down_n);
+        t1 = __fmul_rn(t1, down_n);
+        t0 = __fmul_rn(t0, batch_scale);
+        t1 = __fmul_rn(t1, batch_scale);
+        __half2 h = __floats2half2_rn(t0, t1);
+        if (has_bias) h = __hadd2(h, b[j]);
         o[j] = h;
-        running_absmax = __hmax(running_absmax, __habs(h));
+        if (ABSMAX) running_absmax = __hmax2(running_absmax, __habs2(h));
     }
     return ov;
+}
+
+// Epilogue staging: every epilogue warp owns two 4 KiB buffers (32 rows x 128 bytes, 128-byte swizzle) that it
+// fills from its 32 TMEM lanes and hands to the TMA unit, which writes whole 128-byte lines and clips the box
+// at the matrix bounds (no per-element predicates, no partial sectors).
+constexpr int EPI_STAGE_BYTES = 4 * 2 * 4096;
+
+// Drains this warp's 32 lanes x BN accumulator columns (TMEM address taddr_row) for output rows
+// row0 .. row0 + 31 and columns n_base .. n_base + BN - 1: RAW_I32, DEQUANT_F16 or DEQUANT_F16_REQUANT_I8.
+// `stage` = shared-memory address of the warp's two buffers; `sel` counts the slabs stored so far.
+template <int BN>
+__device__ __forceinline__ void drain_tile(const KernelParams& p, const CUtensorMap* tmap_out, uint32_t taddr_row,
+                                           int row0, int n_base, int lane, uint32_t stage, uint32_t& sel) {
+    const int row = row0 + lane;
+    const bool row_ok = row < p.M;
+    const uint32_t my_row = (uint32_t)lane * 128u, sw = (uint32_t)(lane & 7);
+    if (p.mode == EPI_RAW_I32) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+            const int n0 = n_base + c0;
+            if (n0 >= p.N) break; // warp-uniform
+            uint32_t acc[32];
+            ptx::tmem_ld_32x32(taddr_row + c0, acc);
+            ptx::tmem_ld_wait();
+            if (p.raw_affine) {
+                const int32_t* old = reinterpret_cast<const int32_t*>(p.out) + (int64_t)row * p.ldc + n0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    if (n0 + j >= p.N) break; // N % 8 == 0: groups of four are all-or-nothing
+                    int4 b4 = make_int4(0, 0, 0, 0), o4 = make_int4(0, 0, 0, 0);
+                    if (p.raw_bias != nullptr) b4 = *reinterpret_cast<const int4*>(p.raw_bias + n0 + j);
+                    if (p.raw_beta != 0 && row_ok) o4 = *reinterpret_cast<const int4*>(old + j);
+                    acc[j] = (uint32_t)p.raw_alpha * acc[j] + (uint32_t)p.raw_beta * (uint32_t)o4.x + (uint32_t)b4.x;
+                    acc[j + 1] = (uint32_t)p.raw_alpha * acc[j + 1] + (uint32_t)p.raw_beta * (uint32_t)o4.y + (uint32_t)b4.y;
+                    acc[j + 2] = (uint32_t)p.raw_alpha * acc[j + 2] + (uint32_t)p.raw_beta * (uint32_t)o4.z + (uint32_t)b4.z;
+                    acc[j + 3] = (uint32_t)p.raw_alpha * acc[j + 3] + (uint32_t)p.raw_beta * (uint32_t)o4.w + (uint32_t)b4.w;
+                }
+            }
+            const uint32_t buf = stage + (sel & 1u) * 4096u;
+            if (lane == 0) ptx::bulk_wait_group_read<1>(); // the store that last used this buffer has read it
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                ptx::st_shared_v4(buf + my_row + (((uint32_t)j ^ sw) << 4), make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+                ptx::tma_store_2d(tmap_out, buf, n0, row0);
+                ptx::bulk_commit_group();
+            }
+            ++sel;
+        }
+        return;
+    }
+    const bool has_bias = p.bias != nullptr;
+    const bool want_absmax = p.mode == EPI_DEQUANT_F16_REQUANT_I8;
+    const float batch_scale = row_ok ? __fmul_rn(__half2float(p.scale_m[row]), p.down_m) : 0.0f;
+    __half2 absmax2 = __float2half2_rn(0.0f);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 64) {
+        const int n0 = n_base + c0;
+        if (n0 >= p.N) break; // warp-uniform
+        const uint32_t buf = stage + (sel & 1u) * 4096u;
+        if (lane == 0) ptx::bulk_wait_group_read<1>();
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int nn = n0 + 32 * h;
+            if (nn >= p.N) break; // warp-uniform; the box is clipped at column N
+            uint32_t acc[32];
+            ptx::tmem_ld_32x32(taddr_row + c0 + 32 * h, acc);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+                if (nn + j >= p.N) break;
+                const uint4 v = want_absmax ? dequant8<true>(acc + j, p.scale_n + nn + j, p.bias + nn + j, p.down_n, batch_scale, has_bias, absmax2)
+                                            : dequant8<false>(acc + j, p.scale_n + nn + j, p.bias + nn + j, p.down_n, batch_scale, has_bias, absmax2);
+                ptx::st_shared_v4(buf + my_row + (((uint32_t)(4 * h + (j >> 3)) ^ sw) << 4), v);
+            }
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && row0 < p.M) {
+            ptx::tma_store_2d(tmap_out, buf, n0, row0);
+            ptx::bulk_commit_group();
+        }
+        ++sel;
+    }
+    if (want_absmax && row_ok) {
+        const __half m = __hmax(__low2half(absmax2), __high2half(absmax2));
+        atomicMax(p.row_absmax_bits + row, __float_as_uint(__half2float(m)));
+    }
 }
 
 template <int BN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                       const KernelParams p) {
+                       const __grid_constant__ CUtensorMap tmap_out, const KernelParams p) {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(1024) uint8_t epi_stage[EPI_STAGE_BYTES];
     __shared__ __align__(8) uint64_t full_bar[C::STAGES];
     __shared__ __align__(8) uint64_t empty_bar[C::STAGES];
     __shared__ __align__(8) uint64_t acc_full_bar[2];
@@ -188,12 +291,9 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     } else {
         // ------------------------------------------------------------------ epilogue
         const int quarter = warp & 3; // TMEM lanes [32 * quarter, 32 * quarter + 32) belong to this warp
-        // with more than four epilogue warps, warps sharing a lane quarter split the tile's columns
-        constexpr int COL_GROUPS = EPI_WARPS / 4;
-        constexpr int GROUP_COLS = (BN / COL_GROUPS) >= 32 ? BN / COL_GROUPS : BN;
-        const int col_begin = ((warp - 2) >> 2) * GROUP_COLS;
-        const int col_end = col_begin + GROUP_COLS < BN ? col_begin + GROUP_COLS : BN;
-        const bool has_bias = p.bias != nullptr;
+        const uint32_t stage = ptx::smem_addr(epi_stage) + (uint32_t)(warp - 2) * 8192u;
+        uint32_t sel = 0;
+        if (lane == 0) ptx::prefetch_tensormap(&tmap_out);
         int it = 0;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
             const int m_tile = tile % p.num_m_tiles;
@@ -201,45 +301,15 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
             if (!ptx::mbar_wait(ptx::smem_addr(&acc_full_bar[buf]), acc_phase, p.status, ST_EPI_TIMEOUT)) break;
             ptx::tc_fence_after();
-
-            const int row = m_tile * BM + quarter * 32 + lane;
-            const bool row_ok = row < p.M;
-            float batch_scale = 0.0f;
-            if (p.mode != EPI_RAW_I32 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
-            __half absmax = __float2half_rn(0.0f);
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * BN;
-
-#pragma unroll 1
-            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
-                const int n0 = n_tile * BN + c0;
-                if (n0 >= p.N) break; // warp-uniform
-                uint32_t acc[32];
-                ptx::tmem_ld_32x32(taddr_row + c0, acc);
-                ptx::tmem_ld_wait();
-                if (!row_ok) continue;
-                if (p.mode == EPI_RAW_I32) {
-                    int32_t* dst = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldc + n0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        if (n0 + j < p.N) // N % 8 == 0, so groups of 4 are all-or-nothing
-                            *reinterpret_cast<uint4*>(dst + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-                } else {
-                    half* dst = reinterpret_cast<half*>(p.out) + (int64_t)row * p.ldc + n0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8)
-                        if (n0 + j < p.N)
-                            *reinterpret_cast<uint4*>(dst + j) =
-                                dequant8(acc + j, p.scale_n + n0 + j, p.bias + n0 + j, p.down_n, batch_scale, has_bias, absmax);
-                }
-            }
-            if (p.mode == EPI_DEQUANT_F16_REQUANT_I8 && row_ok)
-                atomicMax(p.row_absmax_bits + row, __float_as_uint(__half2float(absmax)));
+            drain_tile<BN>(p, &tmap_out, taddr_row, m_tile * BM + quarter * 32, n_tile * BN, lane, stage, sel);
 
             // accumulator buffer drained: hand it back to the MMA warp
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&acc_empty_bar[buf]));
         }
+        if (lane == 0) ptx::bulk_wait_group<0>(); // the staging buffers must outlive the stores that read them
     }
 
     ptx::tc_fence_before();
@@ -274,7 +344,7 @@ struct PairCfg {
 template <int EW>
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const KernelParams p) {
+                            const __grid_constant__ CUtensorMap tmap_out, const KernelParams p) {
     using C = PairCfg;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[C::STAGES];   // used in the leader: both CTAs' tiles have landed
@@ -282,9 +352,10 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     __shared__ __align__(8) uint64_t acc_full_bar[2];       // per CTA: accumulator buffer complete
     __shared__ __align__(8) uint64_t acc_empty_bar[2];      // used in the leader: both CTAs drained the buffer
     __shared__ uint32_t tmem_base_slot;
-    // EPI_PUSH_I32: one 32 x 32 int32 block per epilogue warp, to turn "one row per lane" into
-    // 128-byte contiguous row segments before the stores leave for another GPU
-    __shared__ __align__(16) uint4 push_stage[EW == 4 ? 4 : 1][256];
+    // Staging of the four-warp epilogues (two 4 KiB buffers per warp): TMA-store source of the fp16 / int32
+    // outputs; in EPI_PUSH_I32 a 32 x 32 int32 block per warp, to turn "one row per lane" into 128-byte
+    // contiguous row segments before the stores leave for another GPU.  Unused by the eight-warp SwiGLU form.
+    __shared__ __align__(1024) uint8_t epi_stage[EW == 4 ? EPI_STAGE_BYTES : 1024];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -389,8 +460,8 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         const int quarter = warp & 3;
         constexpr int COL_GROUPS = EW / 4;
         const int col_group = (warp - 2) >> 2;
-        const int col_begin = col_group * (C::BN / COL_GROUPS), col_end = col_begin + C::BN / COL_GROUPS;
-        const bool has_bias = p.bias != nullptr;
+        uint32_t sel = 0;
+        if (EW == 4 && lane == 0 && p.mode != EPI_PUSH_I32) ptx::prefetch_tensormap(&tmap_out);
         int it = 0;
         for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
             const int m_tile = tile % p.num_m_tiles;
@@ -402,8 +473,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             const int row = m_tile * 256 + (int)rank * BM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
             float batch_scale = 0.0f;
-            if (p.mode != EPI_RAW_I32 && p.mode != EPI_PUSH_I32 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
-            __half absmax = __float2half_rn(0.0f);
+            if (p.mode == EPI_SWIGLU_F16 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::BN;
 
             if (p.mode == EPI_SWIGLU_F16) {
@@ -452,7 +522,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                 // row l of the warp's 32 x 32 block; after the exchange through shared memory lane l
                 // stores 16 bytes of row 4 i + l / 8 (i = 0..7), so a warp-wide store covers four
                 // complete 128-byte lines.
-                uint4* tr = push_stage[EW == 4 ? warp - 2 : 0];
+                uint4* tr = reinterpret_cast<uint4*>(epi_stage + (EW == 4 ? (warp - 2) * 8192 : 0));
                 const int sub = lane >> 3, chunk = lane & 7;
                 int32_t* dst_row[8];
 #pragma unroll
@@ -490,37 +560,16 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                 continue;
             }
 
-#pragma unroll 1
-            for (int c0 = col_begin; c0 < col_end; c0 += 32) {
-                const int n0 = n_tile * C::BN + c0;
-                if (n0 >= p.N) break; // warp-uniform
-                uint32_t acc[32];
-                ptx::tmem_ld_32x32(taddr_row + c0, acc);
-                ptx::tmem_ld_wait();
-                if (!row_ok) continue;
-                if (p.mode == EPI_RAW_I32) {
-                    int32_t* dst = reinterpret_cast<int32_t*>(p.out) + (int64_t)row * p.ldc + n0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 4)
-                        if (n0 + j < p.N)
-                            *reinterpret_cast<uint4*>(dst + j) = make_uint4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-                } else {
-                    half* dst = reinterpret_cast<half*>(p.out) + (int64_t)row * p.ldc + n0;
-#pragma unroll
-                    for (int j = 0; j < 32; j += 8)
-                        if (n0 + j < p.N)
-                            *reinterpret_cast<uint4*>(dst + j) =
-                                dequant8(acc + j, p.scale_n + n0 + j, p.bias + n0 + j, p.down_n, batch_scale, has_bias, absmax);
-                }
-            }
-            if (p.mode == EPI_DEQUANT_F16_REQUANT_I8 && row_ok)
-                atomicMax(p.row_absmax_bits + row, __float_as_uint(__half2float(absmax)));
+            if (EW == 4)
+                drain_tile<C::BN>(p, &tmap_out, taddr_row, m_tile * 256 + (int)rank * BM + quarter * 32, n_tile * C::BN, lane,
+                                  ptx::smem_addr(epi_stage) + (uint32_t)(warp - 2) * 8192u, sel);
 
             // this CTA's half of the accumulator buffer is drained: tell the leader's MMA thread
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
         }
+        if (EW == 4 && lane == 0) ptx::bulk_wait_group<0>(); // the staging buffers must outlive the stores that read them
     }
 
     // Neither CTA may leave while its partner can still read its shared memory or signal its barriers.
@@ -564,10 +613,38 @@ bool make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t 
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Output matrix [M, N] with leading dimension ldc (elements of elem_bytes = 2 or 4); box = 32 rows x 128 bytes,
+// 128-byte swizzle: what one epilogue warp stages per store.
+bool make_output_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t ldc, int elem_bytes) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+    const cuuint64_t strides[1] = {(cuuint64_t)(ldc * elem_bytes)};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 32u};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_INT32, 2, base, dims, strides, box,
+              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+void fill_common(KernelParams& p, const GemmArgs& a, unsigned int* status) {
+    p.M = (int32_t)a.M; p.N = (int32_t)a.N;
+    p.num_k_blocks = (int32_t)((a.K + BK - 1) / BK);
+    p.mode = a.mode;
+    p.out = a.out; p.ldc = a.ldc;
+    p.scale_m = a.scale_m; p.scale_n = a.scale_n; p.bias = a.bias;
+    p.down_m = a.down_m; p.down_n = a.down_n;
+    p.row_absmax_bits = a.row_absmax_bits;
+    p.status = status;
+    p.raw_alpha = a.raw_alpha; p.raw_beta = a.raw_beta; p.raw_bias = a.raw_bias;
+    p.raw_affine = (a.raw_alpha != 1 || a.raw_beta != 0 || a.raw_bias != nullptr) ? 1 : 0;
+}
+
 struct DeviceInfo {
     bool ready = false;
     int sms = 0;
     unsigned int* status = nullptr;
+    cudaStream_t status_stream = nullptr; // private non-blocking stream: reading the status word waits for nobody
 };
 std::mutex g_dev_mutex;
 DeviceInfo g_dev[64];
@@ -589,7 +666,8 @@ const DeviceInfo* device_info() {
         void* addr = nullptr;
         if (cudaGetSymbolAddress(&addr, g_gemm_status) != cudaSuccess) return nullptr;
         d.status = static_cast<unsigned int*>(addr);
-        if (!set_smem_attr<256>() || !set_smem_attr<128>() || !set_smem_attr<64>() || !set_smem_attr<32>()) return nullptr;
+        if (cudaStreamCreateWithFlags(&d.status_stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        if (!set_smem_attr<256>() || !set_smem_attr<128>() || !set_smem_attr<64>()) return nullptr;
         if (cudaFuncSetAttribute(gemm_i8_tcgen05_pair_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  PairCfg::SMEM_BYTES) != cudaSuccess) return nullptr;
         if (cudaFuncSetAttribute(gemm_i8_tcgen05_pair_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -601,42 +679,34 @@ const DeviceInfo* device_info() {
 
 template <int BN>
 int32_t launch_bn(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev) {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
     if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, BN)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
+    if (!make_output_map(&tc, a.out, a.M, a.N, a.ldc, a.mode == EPI_RAW_I32 ? 4 : 2))
+        return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (C) encode failed");
     KernelParams p{};
-    p.M = (int32_t)a.M; p.N = (int32_t)a.N;
+    fill_common(p, a, dev.status);
     p.num_m_tiles = (int32_t)((a.M + BM - 1) / BM);
     p.num_n_tiles = (int32_t)((a.N + BN - 1) / BN);
-    p.num_k_blocks = (int32_t)((a.K + BK - 1) / BK);
-    p.mode = a.mode;
-    p.out = a.out; p.ldc = a.ldc;
-    p.scale_m = a.scale_m; p.scale_n = a.scale_n; p.bias = a.bias;
-    p.down_m = a.down_m; p.down_n = a.down_n;
-    p.row_absmax_bits = a.row_absmax_bits;
-    p.status = dev.status;
     const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
     const int grid = (int)(tiles < dev.sms ? tiles : dev.sms);
-    gemm_i8_tcgen05_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, p);
+    gemm_i8_tcgen05_kernel<BN><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(ta, tb, tc, p);
     return check_launch("gemm_i8_tcgen05");
 }
 
 // 256 x 256 tiles on CTA pairs (clusters of two), persistent: one pair per two SMs.
 int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev) {
-    CUtensorMap ta, tb;
+    CUtensorMap ta, tb, tc;
     if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
     if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, PairCfg::HALF_N)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
+    memset(&tc, 0, sizeof(tc)); // the SwiGLU and push epilogues store with their own instructions and never touch it
+    if (a.mode != EPI_SWIGLU_F16 && a.mode != EPI_PUSH_I32 &&
+        !make_output_map(&tc, a.out, a.M, a.N, a.ldc, a.mode == EPI_RAW_I32 ? 4 : 2))
+        return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (C) encode failed");
     KernelParams p{};
-    p.M = (int32_t)a.M; p.N = (int32_t)a.N;
+    fill_common(p, a, dev.status);
     p.num_m_tiles = (int32_t)((a.M + 255) / 256);
     p.num_n_tiles = (int32_t)((a.N + PairCfg::BN - 1) / PairCfg::BN);
-    p.num_k_blocks = (int32_t)((a.K + BK - 1) / BK);
-    p.mode = a.mode;
-    p.out = a.out; p.ldc = a.ldc;
-    p.scale_m = a.scale_m; p.scale_n = a.scale_n; p.bias = a.bias;
-    p.down_m = a.down_m; p.down_n = a.down_n;
-    p.row_absmax_bits = a.row_absmax_bits;
-    p.status = dev.status;
     p.act_dim = 0; p.beta = a.beta;
     for (int i = 0; i < kMaxPeers; ++i) p.push_base[i] = a.push_base[i];
     p.push_rows = a.push_rows; p.push_rank = a.push_rank;
@@ -661,8 +731,8 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = wide_epilogue ? cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<8>, ta, tb, p)
-                                        : cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<4>, ta, tb, p);
+    const cudaError_t e = wide_epilogue ? cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<8>, ta, tb, tc, p)
+                                        : cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<4>, ta, tb, tc, p);
     if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "pair GEMM launch failed: %s", cudaGetErrorString(e));
     return RC_SUCCESS;
 }
@@ -687,28 +757,23 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
 
     // Tile width: the widest tile that still gives every SM work.
     const int64_t m_tiles = (a.M + BM - 1) / BM;
-    int bn = 32;
-    const int cand[3] = {256, 128, 64};
-    for (int i = 0; i < 3; ++i) {
-        if (m_tiles * ((a.N + cand[i] - 1) / cand[i]) >= dev->sms) { bn = cand[i]; break; }
-    }
-    switch (bn) {
-    case 256: return launch_bn<256>(stream, a, *dev);
-    case 128: return launch_bn<128>(stream, a, *dev);
-    case 64: return launch_bn<64>(stream, a, *dev);
-    default: return launch_bn<32>(stream, a, *dev);
-    }
+    if (m_tiles * ((a.N + 255) / 256) >= dev->sms) return launch_bn<256>(stream, a, *dev);
+    if (m_tiles * ((a.N + 127) / 128) >= dev->sms) return launch_bn<128>(stream, a, *dev);
+    return launch_bn<64>(stream, a, *dev);
 }
 
 int32_t gemm_status(int32_t reset) {
     const DeviceInfo* dev = device_info();
     if (!dev) return -1;
+    // Reads the word as it is now, on a private stream: no other stream of the device is waited for.  A caller
+    // that asks about particular launches synchronises the streams it launched them on first.
     unsigned int v = 0;
-    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    if (cudaMemcpy(&v, dev->status, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (cudaMemcpyAsync(&v, dev->status, sizeof(v), cudaMemcpyDeviceToHost, dev->status_stream) != cudaSuccess ||
+        cudaStreamSynchronize(dev->status_stream) != cudaSuccess)
+        return -1;
     if (reset && v != 0) {
-        unsigned int z = 0;
-        cudaMemcpy(dev->status, &z, sizeof(z), cudaMemcpyHostToDevice);
+        cudaMemsetAsync(dev->status, 0, sizeof(v), dev->status_stream);
+        cudaStreamSynchronize(dev->status_stream);
     }
     return (int32_t)v;
 }

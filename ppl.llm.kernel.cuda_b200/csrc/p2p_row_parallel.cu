@@ -125,7 +125,7 @@ __device__ __forceinline__ void wait_flags(uint32_t* flag_page, int flag_row, in
 // the dequant epilogue: 8 columns per item.  Writes the rows into the caller's output and into the
 // staging copy (both with leading dimension `dim`).
 __global__ void __launch_bounds__(256)
-p2p_reduce_dequant_kernel(uint32_t* flag_page, int flag_row, int size, const int32_t* __restrict__ recv,
+p2p_reduce_dequant_kernel(uint32_t* flag_page, int flag_row, int size, const int32_t* recv,
                           int64_t rows, int64_t dim, int64_t col0, int64_t ncols, const half* __restrict__ scale_m,
                           const half* __restrict__ scale_n, const half* __restrict__ bias, float down_m, float down_n,
                           half* __restrict__ out_rows, half* __restrict__ staging) {
@@ -137,18 +137,21 @@ p2p_reduce_dequant_kernel(uint32_t* flag_page, int flag_row, int size, const int
         const int64_t m = i / chunks_per_row;
         const int64_t n = col0 + ((i - m * chunks_per_row) << 3);
         const int32_t* src = recv + m * dim + n;
-        int4 a0 = *reinterpret_cast<const int4*>(src);
-        int4 a1 = *reinterpret_cast<const int4*>(src + 4);
+        // recv is written by other GPUs while this kernel is resident (it only reads after the acquire
+        // above): relaxed system-scope loads, never the read-only path
+        uint4 a0 = ld_peer_v4(reinterpret_cast<const uint4*>(src));
+        uint4 a1 = ld_peer_v4(reinterpret_cast<const uint4*>(src + 4));
         for (int s = 1; s < size; ++s) {
-            const int4 b0 = *reinterpret_cast<const int4*>(src + s * slice);
-            const int4 b1 = *reinterpret_cast<const int4*>(src + s * slice + 4);
+            const uint4 b0 = ld_peer_v4(reinterpret_cast<const uint4*>(src + s * slice));
+            const uint4 b1 = ld_peer_v4(reinterpret_cast<const uint4*>(src + s * slice + 4));
             a0.x += b0.x; a0.y += b0.y; a0.z += b0.z; a0.w += b0.w;
             a1.x += b1.x; a1.y += b1.y; a1.z += b1.z; a1.w += b1.w;
         }
         const float bs = __fmul_rn(__half2float(scale_m[m]), down_m);
         const uint4 snv = *reinterpret_cast<const uint4*>(scale_n + n);
         const half* sn = reinterpret_cast<const half*>(&snv);
-        const int32_t a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        const int32_t a[8] = {(int32_t)a0.x, (int32_t)a0.y, (int32_t)a0.z, (int32_t)a0.w,
+                              (int32_t)a1.x, (int32_t)a1.y, (int32_t)a1.z, (int32_t)a1.w};
         uint4 ov;
         half* o = reinterpret_cast<half*>(&ov);
 #pragma unroll
@@ -457,13 +460,15 @@ int32_t pplb200_p2p_destroy(void* ctx) {
 int32_t pplb200_p2p_status(void* ctx, int32_t reset) {
     Ctx* c = (Ctx*)ctx;
     if (!c) return -1;
+    // read on the context's own (non-blocking) stream: no other stream of the device is waited for
     uint32_t v = 0;
     uint32_t* word = reinterpret_cast<uint32_t*>(c->base) + kStatusWord;
-    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
-    if (cudaMemcpy(&v, word, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (cudaMemcpyAsync(&v, word, 4, cudaMemcpyDeviceToHost, c->side) != cudaSuccess ||
+        cudaStreamSynchronize(c->side) != cudaSuccess)
+        return -1;
     if (reset && v != 0) {
-        const uint32_t z = 0;
-        cudaMemcpy(word, &z, 4, cudaMemcpyHostToDevice);
+        cudaMemsetAsync(word, 0, 4, c->side);
+        cudaStreamSynchronize(c->side);
     }
     return (int32_t)v;
 }

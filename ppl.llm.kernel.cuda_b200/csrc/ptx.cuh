@@ -87,6 +87,26 @@ __device__ __forceinline__ void tma_load_2d_hint(uint32_t dst, const CUtensorMap
         : "memory");
 }
 
+// 2-D tiled store, shared -> global, tracked by the thread's bulk async-group.  The box is clipped at the
+// tensor's bounds; x * element size must be a multiple of 16 bytes and neither coordinate negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// returns once at most N of this thread's bulk groups still have to READ their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N> __device__ __forceinline__ void bulk_wait_group() {
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+// orders this thread's earlier generic-proxy writes to shared memory before later async-proxy (TMA) reads of them
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
 // ---- tcgen05 / TMEM ---------------------------------------------------------------------------
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) { // whole warp

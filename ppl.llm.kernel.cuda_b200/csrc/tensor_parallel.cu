@@ -63,34 +63,6 @@ using namespace pplb200;
 
 namespace {
 
-// Side stream and events used to overlap the reduction of one row chunk with the GEMM of the next.
-// Created once per device on first use (never on later calls); the caller's stream stays the
-// only stream the caller has to synchronise with.
-struct Overlap {
-    bool ready = false;
-    cudaStream_t comm = nullptr;
-    cudaEvent_t fork = nullptr, join = nullptr;
-    cudaEvent_t gemm_done[8] = {};
-};
-std::mutex g_overlap_mutex;
-Overlap g_overlap[64];
-
-Overlap* overlap_for_current_device() {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-    std::lock_guard<std::mutex> lock(g_overlap_mutex);
-    Overlap& o = g_overlap[dev];
-    if (!o.ready) {
-        if (cudaStreamCreateWithFlags(&o.comm, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
-        if (cudaEventCreateWithFlags(&o.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
-        if (cudaEventCreateWithFlags(&o.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
-        for (auto& e : o.gemm_done)
-            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return nullptr;
-        o.ready = true;
-    }
-    return &o;
-}
-
 int32_t nccl_fail(const char* what, ncclResult_t r) {
     return fail(RC_DEVICE_RUNTIME_ERROR, "%s failed: %s", what, nccl_api().ok ? nccl_api().GetErrorString(r) : "NCCL not loaded");
 }
@@ -179,40 +151,27 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* i
     // Preferred schedule: the int32 partials are reduce-scattered over the ranks (each rank receives
     // the exact sums of its row slice), the slice is dequantized once, and the fp16 slices are
     // all-gathered -- 25 % less wire traffic than an int32 all-reduce and the epilogue work is split
-    // over the ranks.  With more than one row chunk the collectives of chunk c run on a side stream
-    // under the GEMM of chunk c + 1.
-    // One chunk measured fastest when the calls are enqueued eagerly (each extra chunk costs three more
-    // host-side enqueues); the chunked schedule is kept for callers that replay the sequence.
-    const int chunks = 1;
-    Overlap* ov = (M % size == 0) ? overlap_for_current_device() : nullptr;
-    if (ov != nullptr) {
-        const int64_t Mc = M / chunks, Ms = Mc / size; // rows per chunk, rows per rank slice
-        const int8_t* in8 = (const int8_t*)input;
+    // over the ranks.  Everything is enqueued on the caller's stream: the library owns no stream or
+    // event on this path, so concurrent callers on one device cannot disturb each other and the
+    // sequence can be captured like any other stream work.  (A row-chunked form with the collectives
+    // of chunk c on a second stream under the GEMM of chunk c + 1 measured slower on 2, 4 and 8
+    // GPUs -- a persistent GEMM leaves the collectives' kernels no SMs -- and was removed.)
+    if (M % size == 0) {
+        const int64_t Ms = M / size; // rows per rank slice
         int32_t* acc = (int32_t*)quant_buffer;
         half* out16 = (half*)output;
-        if (cudaEventRecord(ov->fork, stream) != cudaSuccess || cudaStreamWaitEvent(ov->comm, ov->fork, 0) != cudaSuccess)
-            return fail(RC_DEVICE_RUNTIME_ERROR, "stream fork failed");
-        for (int c = 0; c < chunks; ++c) {
-            int32_t* acc_c = acc + (int64_t)c * Mc * N;
-            int32_t rc = gemm_entry(stream, in8 + (int64_t)c * Mc * lda, lda, weight, Kw, Mc, N, Kw, EPI_RAW_I32, nullptr,
-                                    nullptr, nullptr, 0.f, 0.f, 0.f, ws, ws_bytes, acc_c, N, nullptr, nullptr);
-            if (rc != RC_SUCCESS) return rc;
-            if (cudaEventRecord(ov->gemm_done[c], stream) != cudaSuccess ||
-                cudaStreamWaitEvent(ov->comm, ov->gemm_done[c], 0) != cudaSuccess)
-                return fail(RC_DEVICE_RUNTIME_ERROR, "stream hand-over failed");
-            int32_t* mine = acc_c + (int64_t)rank * Ms * N; // reduce-scatter in place: this rank's slice
-            ncclResult_t r = nccl_api().ReduceScatter(acc_c, mine, (size_t)(Ms * N), ncclInt32, ncclSum, (ncclComm_t)nccl_comm, ov->comm);
-            if (r != ncclSuccess) return nccl_fail("ncclReduceScatter(int32)", r);
-            const int64_t row0 = (int64_t)c * Mc + (int64_t)rank * Ms;
-            rc = launch_dequantize(ov->comm, mine, (const half*)optional_bias, (const half*)scale_M + row0,
-                                   (const half*)scale_N, Ms, N, down_scale_M, down_scale_N, LAYOUT_ROW_MAJOR, out16 + row0 * N);
-            if (rc != RC_SUCCESS) return rc;
-            r = nccl_api().AllGather(out16 + row0 * N, out16 + (int64_t)c * Mc * N, (size_t)(Ms * N), ncclHalf, (ncclComm_t)nccl_comm, ov->comm);
-            if (r != ncclSuccess) return nccl_fail("ncclAllGather(fp16)", r);
-        }
-        if (cudaEventRecord(ov->join, ov->comm) != cudaSuccess || cudaStreamWaitEvent(stream, ov->join, 0) != cudaSuccess)
-            return fail(RC_DEVICE_RUNTIME_ERROR, "stream join failed");
-        return RC_SUCCESS;
+        int32_t rc = gemm_entry(stream, input, lda, weight, Kw, M, N, Kw, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f,
+                                0.f, ws, ws_bytes, acc, N, nullptr, nullptr);
+        if (rc != RC_SUCCESS) return rc;
+        int32_t* mine = acc + (int64_t)rank * Ms * N; // reduce-scatter in place: this rank's slice
+        ncclResult_t r = nccl_api().ReduceScatter(acc, mine, (size_t)(Ms * N), ncclInt32, ncclSum, (ncclComm_t)nccl_comm, stream);
+        if (r != ncclSuccess) return nccl_fail("ncclReduceScatter(int32)", r);
+        const int64_t row0 = (int64_t)rank * Ms;
+        rc = launch_dequantize(stream, mine, (const half*)optional_bias, (const half*)scale_M + row0, (const half*)scale_N,
+                               Ms, N, down_scale_M, down_scale_N, LAYOUT_ROW_MAJOR, out16 + row0 * N);
+        if (rc != RC_SUCCESS) return rc;
+        r = nccl_api().AllGather(out16 + row0 * N, out16, (size_t)(Ms * N), ncclHalf, (ncclComm_t)nccl_comm, stream);
+        return r == ncclSuccess ? RC_SUCCESS : nccl_fail("ncclAllGather(fp16)", r);
     }
 
     // Fallback (M not divisible by the number of ranks): int32 all-reduce, then the epilogue on every rank.

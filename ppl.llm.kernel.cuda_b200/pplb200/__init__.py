@@ -41,6 +41,7 @@ EXPORTS = [
     "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
     "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
     "pplb200_i8i8_minmax_quantize_fp16_p2p",
+    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -88,6 +89,9 @@ def _load():
     lib.pplb200_p2p_status.argtypes = [vp, i32]
     lib.pplb200_i8i8_row_parallel_linear_p2p.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32, vp]
     lib.pplb200_i8i8_minmax_quantize_fp16_p2p.argtypes = [vp, vp, vp, i64, i64, f32, i32, vp, vp]
+    lib.pplb200_i8i8_gemm_i32.argtypes = [vp, vp, i64, vp, i64, i64, i64, i64, i32, i32, vp, vp, i64]
+    lib.pplb200_probe_tensor_peak.argtypes = [vp, i32, i32, vp]
+    lib.pplb200_probe_stream_read.argtypes = [vp, vp, i64, vp]
     lib.pplb200_nccl_get_unique_id.argtypes = [vp]
     lib.pplb200_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
     lib.pplb200_nccl_comm_destroy.argtypes = [vp]
@@ -250,6 +254,17 @@ def gemm_i8i8(a, b, mode=EPI_RAW_I32, scale_m=None, scale_n=None, bias=None, dow
                                  _ptr(scale_n), _ptr(bias), down_m, down_n, requant_up_scale, _ptr(ws),
                                  0 if ws is None else ws.numel(), _ptr(y), y.stride(0), _ptr(yq), _ptr(ys)))
     return y if mode != EPI_DEQUANT_F16_REQUANT_I8 else (y, yq, ys)
+
+
+def gemm_i8i8i32(a, b, alpha=1, beta=0, bias_i32=None, out=None):
+    """C int32 [M,N] = alpha * (a int8 [M,K] @ b int8 [N,K]^T) + beta * C + bias_i32[n] (wrapping int32)."""
+    import torch
+    M, K = a.shape
+    N = b.shape[0]
+    c = out if out is not None else torch.zeros((M, N), dtype=torch.int32, device=a.device)
+    _check(lib.pplb200_i8i8_gemm_i32(_stream(), _ptr(a), a.stride(0), _ptr(b), b.stride(0), M, N, K, alpha, beta,
+                                     _ptr(bias_i32), _ptr(c), c.stride(0)))
+    return c
 
 
 def gemm_requant_static_scratch(a, b, scale_m, scale_n, bias=None, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE,
@@ -417,3 +432,83 @@ def minmax_quantize_fp16_p2p(p2p, x_shard, up_scale=TOKEN_UP_SCALE, out=None, sc
     _check(lib.pplb200_i8i8_minmax_quantize_fp16_p2p(_stream(), p2p.ctx, _ptr(x_shard), M, Kw, up_scale, phases,
                                                      _ptr(out), _ptr(scale)))
     return out, scale
+
+
+def _probe_record(t):
+    import struct
+    cycles, nanos, status, _ = struct.unpack("<QQII", bytes(t.cpu().numpy().tobytes()))
+    return cycles, nanos, status
+
+
+def tensor_peak_probe(mmas_per_cta=8192, sustained_launches=100):
+    """int8 tcgen05 issue-rate ceiling of the current device: all SMs issue kind::i8 MMAs on operands that stay
+    in shared memory.  "tops" is the best single launch of the CTA-pair form (the shape the prefill GEMM uses);
+    "sustained_tops" the rate over `sustained_launches` launches back to back (tens of milliseconds, long
+    enough for the power limit to pull the clock down)."""
+    import torch
+    rec = torch.zeros((24,), dtype=torch.uint8, device="cuda")
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    out = {}
+    for pairs in (0, 1):
+        ctas = sms if not pairs else sms // 2
+        ops = 2.0 * (256 if pairs else 128) * 256 * 32 * mmas_per_cta * ctas
+        best, mhz = None, None
+        _check(lib.pplb200_probe_tensor_peak(_stream(), pairs, mmas_per_cta, _ptr(rec)))  # warm-up, module load
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _check(lib.pplb200_probe_tensor_peak(_stream(), pairs, mmas_per_cta, _ptr(rec)))
+            e1.record()
+            torch.cuda.synchronize()
+            cycles, nanos, status = _probe_record(rec)
+            if status:
+                raise RuntimeError("tensor peak probe: a bounded wait gave up")
+            ms = e0.elapsed_time(e1)
+            if best is None or ms < best:
+                best, mhz = ms, cycles / max(nanos, 1) * 1e3
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(sustained_launches):
+            _check(lib.pplb200_probe_tensor_peak(_stream(), pairs, mmas_per_cta, _ptr(rec)))
+        e1.record()
+        torch.cuda.synchronize()
+        cycles, nanos, _ = _probe_record(rec)
+        sus = e0.elapsed_time(e1) / sustained_launches
+        key = "pair" if pairs else "single"
+        out[key] = {"tops": ops / (best * 1e-3) / 1e12, "launch_ms": best, "sm_mhz": round(mhz, 1),
+                    "sustained_tops": ops / (sus * 1e-3) / 1e12, "sustained_sm_mhz": round(cycles / max(nanos, 1) * 1e3, 1)}
+    top = max(out["pair"]["tops"], out["single"]["tops"])
+    return {"tops": top, "sustained_tops": max(out["pair"]["sustained_tops"], out["single"]["sustained_tops"]),
+            "how": "tcgen05.mma kind::i8, operands resident in shared memory, no loads; %d MMAs per CTA, all SMs; "
+                   "best of 5 launches, SM clock read inside the kernel; sustained = %d launches back to back"
+                   % (mmas_per_cta, sustained_launches),
+            "cta_group_2_m256_n256": out["pair"], "cta_group_1_m128_n256": out["single"]}
+
+
+def stream_read_probe(sizes=(16 << 20, 48 << 20, 384 << 20), pool_bytes=1536 << 20, reps=12):
+    """Single-launch read-only bulk-copy stream of `size` bytes, each launch on a different slice of a pool larger
+    than L2 (so the bytes come from HBM).  Returns per size the median launch time and GB/s."""
+    import torch
+    pool = torch.empty((pool_bytes,), dtype=torch.uint8, device="cuda")
+    pool.fill_(1)
+    rec = torch.zeros((24,), dtype=torch.uint8, device="cuda")
+    out = {}
+    for size in sizes:
+        slots = max(1, pool_bytes // size)
+        times = []
+        for r in range(reps + 2):
+            off = (r % slots) * size
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _check(lib.pplb200_probe_stream_read(_stream(), ctypes.c_void_p(pool.data_ptr() + off), size, _ptr(rec)))
+            e1.record()
+            torch.cuda.synchronize()
+            if _probe_record(rec)[2]:
+                raise RuntimeError("stream read probe: a bounded wait gave up")
+            if r >= 2:
+                times.append(e0.elapsed_time(e1))
+        times.sort()
+        med = times[len(times) // 2]
+        out["%d MiB" % (size >> 20)] = {"us": round(med * 1e3, 2), "gb_per_s": round(size / (med * 1e-3) / 1e9, 1),
+                                        "note": "includes the 24-byte memset node in front of the launch"}
+    return out

@@ -144,7 +144,7 @@ int main() {
 
 
 def test_workload_generators_are_deterministic_and_shaped():
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     assert [wl.algorithmic_bytes(n) for n in ("c0", "c1", "c2", "c3", "c4")] == \
         [17055744, 56148224, 304131072, 385908736, 838918144]
     x1, x2 = wl.make_activations("c2", 40), wl.make_activations("c2", 300)
@@ -163,3 +163,42 @@ def test_workload_generators_are_deterministic_and_shaped():
     assert wl.shard_rows(22016, 8, 7) == (19264, 22016)
     with pytest.raises(AssertionError):
         wl.shard_rows(10, 4, 0)
+
+
+REFERENCE_DIR = os.environ.get("PPL_LLM_KERNEL_CUDA_REFERENCE", "/root/reference")
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(REFERENCE_DIR, "include")), reason="reference tree not present")
+def test_shadow_headers_coexist_with_the_references_other_operators(tmp_path):
+    """With this repository's include directory placed BEFORE the reference's, translation units of the
+    reference's other linears (fp16 column / row parallel linear, MoE linears, i4f16, f8f8 headers) still compile:
+    the shadowing cublas/gemm.h and cublas/gemm_algo.h keep every declaration those headers and their callers
+    use (fp16 gemm, AlgoCache with its real key / hash types, find_best_algo, MatmulDesc ...)."""
+    src = tmp_path / "mixed.cpp"
+    src.write_text(r'''
+#include "ppl/kernel/llm/cuda/pmx/i8i8/column_parallel_linear.h"   // this repository's
+#include "ppl/kernel/llm/cuda/pmx/i8i8/row_parallel_linear.h"      // this repository's
+#include "ppl/kernel/llm/cuda/pmx/column_parallel_linear.h"        // the reference's (fp16)
+#include "ppl/kernel/llm/cuda/pmx/row_parallel_linear.h"           // the reference's (fp16)
+#include "ppl/kernel/llm/cuda/pmx/moe_column_parallel_linear.h"    // the reference's
+#include "ppl/kernel/llm/cuda/cublas/gemm.h"
+#include <type_traits>
+namespace c = ppl::kernel::llm::cuda::cublas;
+static_assert(std::is_same<c::AlgoCache::key_type, c::AlgoCacheIndex>::value, "AlgoCache key type");
+static_assert(std::is_same<c::AlgoCache::hasher, c::AlgoCacheIndexHash>::value, "AlgoCache hash type");
+int main() {
+    c::AlgoCache cache;
+    c::AlgoCacheIndex idx{};
+    idx.matmul_desc.transa = CUBLAS_OP_T;
+    cache.emplace(idx, cublasLtMatmulAlgo_t{});
+    // the fp16 GEMM and the algorithm search stay declared (their definitions live in the reference's library)
+    auto gemm_ptr = &c::gemm;
+    auto find_ptr = &c::find_best_algo;
+    (void)gemm_ptr; (void)find_ptr;
+    return cache.count(idx) == 1 ? 0 : 1;
+}
+''')
+    obj = tmp_path / "mixed.o"
+    cmd = ["g++", "-std=c++17", "-Wall", "-c", "-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(REFERENCE_DIR, "include"),
+           "-I" + os.path.join(ROOT, "include", "compat"), "-I/usr/local/cuda/include", str(src), "-o", str(obj)]
+    subprocess.run(cmd, check=True)

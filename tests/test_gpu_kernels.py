@@ -275,3 +275,49 @@ def test_gemm_error_codes(cuda):
     assert e.value.rc == pplb200.RC_UNSUPPORTED
     c = pplb200.gemm_i8i8(cuda.zeros((0, 64), dtype=cuda.int8, device="cuda"), b)  # empty M
     assert c.shape == (0, 16)
+
+
+@pytest.mark.parametrize("M,N,K", [(300, 264, 256), (2300, 2120, 272), (130, 1000, 144)])
+def test_gemm_strided_output_is_clipped(cuda, oracle, M, N, K):
+    """Output rows longer than N (ldc > N) and ragged tile edges: the staged epilogue stores must write
+    columns [0, N) of rows [0, M) and nothing else (sentinel columns and a sentinel row stay untouched)."""
+    import pplb200
+    rng = np.random.default_rng(M + N + K)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    sn = (rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)
+    ref = oracle.linear(x, w, sn, None)
+    ldc = N + 72
+    txq, tw = _t(cuda, ref["xq"]), _t(cuda, w)
+    raw = cuda.full((M + 1, ldc), 0x5a5a5a5a, dtype=cuda.int32, device="cuda")
+    pplb200.gemm_i8i8(txq, tw, out=raw[:M, :N])
+    y = cuda.full((M + 1, ldc), 1.5, dtype=cuda.float16, device="cuda")
+    pplb200.gemm_i8i8(txq, tw, mode=pplb200.EPI_DEQUANT_F16, scale_m=_t(cuda, ref["sm"]), scale_n=_t(cuda, sn), out=y[:M, :N])
+    cuda.cuda.synchronize()
+    assert pplb200.gemm_status() == 0
+    assert np.array_equal(raw[:M, :N].cpu().numpy(), ref["acc"])
+    assert bool((raw[:, N:] == 0x5a5a5a5a).all()) and bool((raw[M] == 0x5a5a5a5a).all())
+    assert np.array_equal(oracle.f16_bits(y[:M, :N].cpu().numpy()), oracle.f16_bits(ref["y"]))
+    assert bool((y[:, N:] == 1.5).all()) and bool((y[M] == 1.5).all())
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 256, 128), (100, 1032, 256), (300, 1000, 256), (2300, 2120, 272)])
+@pytest.mark.parametrize("alpha,beta,with_bias", [(1, 0, True), (3, 0, False), (1, 1, False), (-2, 5, True)])
+def test_gemm_i32_alpha_beta_bias(cuda, M, N, K, alpha, beta, with_bias):
+    """The full contract of the reference's gemm_i8i8i32 (src/ppl/kernel/llm/cuda/cublas/gemm.cu:187-188,239-243):
+    C = alpha * (A x B^T) + beta * C + bias[n], wrapping int32."""
+    import pplb200
+    rng = np.random.default_rng(M + N + K + alpha * 7 + beta)
+    a = _t(cuda, rng.integers(-127, 128, (M, K), dtype=np.int8))
+    b = _t(cuda, rng.integers(-127, 128, (N, K), dtype=np.int8))
+    c0 = _t(cuda, rng.integers(-(2 ** 30), 2 ** 30, (M, N), dtype=np.int32))
+    bias = _t(cuda, rng.integers(-(2 ** 20), 2 ** 20, (N,), dtype=np.int32)) if with_bias else None
+    c = c0.clone()
+    pplb200.gemm_i8i8i32(a, b, alpha=alpha, beta=beta, bias_i32=bias, out=c)
+    cuda.cuda.synchronize()
+    assert pplb200.gemm_status() == 0
+    want = alpha * _exact_gemm(cuda, a, b).to(cuda.int64) + beta * c0.to(cuda.int64)
+    if with_bias:
+        want = want + bias.to(cuda.int64)[None, :]
+    want = ((want + 2 ** 31) % (2 ** 32) - 2 ** 31).to(cuda.int32)
+    assert cuda.equal(c, want)

@@ -16,7 +16,7 @@ def _t(torch, a):
 
 
 def _inputs(name):
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     return wl.CONFIGS[name], wl.make_activations(name), wl.make_weights(name), wl.make_column_scales(name), wl.make_bias(name)
 
 
@@ -77,7 +77,7 @@ def test_column_parallel_shards_concatenate(cuda, oracle):
     """N split over 8 'ranks' run one after the other on one GPU: shard outputs == slices of the full output,
     including a shard width (2752) that is not a multiple of the tile width."""
     import pplb200
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     cfg, x, w, sn, bias = _inputs("c2")
     M, K, N = 256, cfg["K"], cfg["N"]
     x = x[:M]

@@ -56,12 +56,12 @@ def _case(torch, pplb200, wl, world, M, K, N, with_bias, rounds=1, seed=0):
     (1, 300, 512, 256, True),       # a single rank: no exchange
 ])
 def test_p2p_row_parallel_matches_unsharded(cuda, pplb200, world, M, K, N, with_bias):
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     _case(cuda, pplb200, wl, world, M, K, N, with_bias)
 
 
 def test_p2p_buffers_are_reusable_across_calls(cuda, pplb200):
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     _case(cuda, pplb200, wl, 4, 768, 1024, 768, True, rounds=4, seed=7)
 
 
@@ -129,7 +129,7 @@ def test_sharded_quantizer_matches_unsharded(cuda, pplb200, world, M, K):
     """Shard maxima are published for every rank first (phase 1), then every rank runs the whole
     operation (phase 3), so no kernel waits for one that has not run.  int8 and scales bit-exact."""
     torch = cuda
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     rng = np.random.default_rng(M + K + world)
     x = rng.standard_normal((M, K)).astype(np.float16)
     x[:, rng.integers(0, K, 8)] *= 30.0   # the row maximum usually sits in one shard only

@@ -19,7 +19,7 @@ def _worker(rank, world, port, out_dir):
     import torch
     import torch.distributed as dist
     import oracle_lib as orc
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
     orc.set_threads(1)
     dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%d" % port, rank=rank, world_size=world)
     rng = np.random.default_rng(11)  # same stream on every rank: replicated inputs

@@ -24,7 +24,7 @@ def _worker(rank, world, tmp):
     import torch
     torch.cuda.set_device(rank)
     import pplb200
-    from pplb200 import workloads as wl
+    import w8a8_workloads as wl
 
     uid_path = os.path.join(tmp, "uid")
     if rank == 0:
