@@ -326,16 +326,32 @@ int32_t pplb200_nccl_comm_destroy(void* comm);
 int32_t pplb200_i8i8_gemm_status(int32_t reset);
 
 /*
+ * Diagnostics (process-wide switch, not thread-safe, off by default): with a non-NULL device array of
+ * 8 x uint64 per CTA (296 CTAs at most), later launches of the CTA-pair GEMM record per CTA the SM cycles
+ * [0] the MMA thread ran, [1] it waited for operand tiles, [2] it waited for a free accumulator,
+ * [3] the TMA thread waited for a free slot, [4] the TMA thread ran, [5] the first epilogue warp waited for
+ * an accumulator, [6] that warp ran.  NULL switches the recording off again.
+ */
+void pplb200_debug_gemm_stall_counters(void* counters);
+
+/*
  * Measurement probes (no counterpart in the reference; they give the roofline denominators that
  * bench.py reports against).  `result24` is a 24-byte device record the launch fills:
  *   uint64 cycles, uint64 nanoseconds (of CTA 0, from first issue to completion), uint32 status, uint32 pad;
  * status != 0 means a bounded wait inside the probe gave up.
  * tensor_peak: every SM issues `mmas_per_cta` back-to-back tcgen05.mma kind::i8 (M 128 x N 256 x K 32 per CTA,
- *   or M 256 x N 256 x K 32 per CTA pair when cta_pairs != 0) on operands resident in shared memory.
+ *   or M 256 x N 256 x K 32 per CTA pair when cta_pairs != 0) on operands resident in shared memory.  With
+ *   stream_src != NULL every CTA also keeps bulk copies from that buffer (stream_bytes, >= 32 KiB) into spare
+ *   shared memory in flight, one 32 KiB copy per four MMAs -- the fill rate of a GEMM main loop -- so the figure
+ *   becomes the ceiling with the copy engine competing for shared memory.  commit_pattern: bits 0-7 = issue a
+ *   tcgen05.commit after every that many MMAs (0: only at the end), bit 8 = plus one to the partner CTA,
+ *   bit 9 = one multicast commit to both CTAs instead: what releasing operand slots costs the issue stream.
  * stream_read: one launch reads `bytes` (a multiple of 32 KiB is used) from `src` with bulk asynchronous copies
  *   and discards them.
  */
-int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream, int32_t cta_pairs, int32_t mmas_per_cta, void* result24);
+int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream, int32_t cta_pairs, int32_t mmas_per_cta, int32_t commit_pattern,
+                                  const void* stream_src,
+                                  int64_t stream_bytes, void* result24);
 int32_t pplb200_probe_stream_read(pplb200_stream_t stream, const void* src, int64_t bytes, void* result24);
 
 /*

@@ -120,5 +120,6 @@ struct GemmArgs {
 int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int* status, bool pdl);
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);
 int32_t gemm_status(int32_t reset);
+void set_stall_counters(void* dev_ptr);
 
 } // namespace pplb200

@@ -18,6 +18,7 @@
 
 #include <mutex>
 #include <string.h>
+#include <stdlib.h>
 
 namespace pplb200 {
 
@@ -46,6 +47,9 @@ struct KernelParams {
     float down_m, down_n;
     uint32_t* row_absmax_bits;
     unsigned int* status;
+    // optional diagnostics: 8 x uint64 per CTA (cycles the MMA / producer / epilogue threads spent in their waits)
+    unsigned long long* stall;
+    int32_t exp_flags; // experiment switches (environment PPLB200_EXP), 0 in production
     // EPI_RAW_I32 with raw_affine != 0: out = raw_alpha * acc + raw_beta * out + raw_bias[n] (wrapping int32)
     int32_t raw_affine, raw_alpha, raw_beta;
     const int32_t* raw_bias;
@@ -258,32 +262,37 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
+        // One thread feeds the tensor cores, so its own instruction stream must stay well under the 128 cycles
+        // an MMA takes: descriptors are a 32-bit add away from the previous ones, and the barrier of the NEXT
+        // stage is polled before the current stage's MMAs are issued, so its latency hides behind them.
         if (lane == 0) {
             constexpr uint32_t idesc = ptx::make_i8_idesc(BM, BN);
+            const uint32_t a_lo0 = ptx::desc_lo_sw128(ring), full0 = ptx::smem_addr(&full_bar[0]), empty0 = ptx::smem_addr(&empty_bar[0]);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int it = 0;
+            bool ready = false;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
                 const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
                 if (!ptx::mbar_wait(ptx::smem_addr(&acc_empty_bar[buf]), acc_phase ^ 1u, p.status, ST_MMA_ACC_TIMEOUT)) break;
                 ptx::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * BN;
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_addr(&full_bar[stage]), phase, p.status, ST_MMA_FULL_TIMEOUT)) {
+                    if (!ready && !ptx::mbar_wait(full0 + stage * 8u, phase, p.status, ST_MMA_FULL_TIMEOUT)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t sa = ring + stage * C::STAGE_BYTES;
-                    const uint64_t adesc = ptx::make_kmajor_sw128_desc(sa);
-                    const uint64_t bdesc = ptx::make_kmajor_sw128_desc(sa + C::A_BYTES);
+                    uint32_t nstage = stage + 1, nphase = phase;
+                    if (nstage == C::STAGES) { nstage = 0; nphase ^= 1u; }
+                    ready = ptx::mbar_try_wait(full0 + nstage * 8u, nphase); // used in the next iteration
+                    const uint32_t a_lo = a_lo0 + stage * (uint32_t)(C::STAGE_BYTES >> 4), b_lo = a_lo + (uint32_t)(C::A_BYTES >> 4);
+                    ptx::mma_i8(tmem_d, ptx::desc_from_lo(a_lo), ptx::desc_from_lo(b_lo), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        // advancing K inside the 128-byte swizzle row: +32 bytes = +2 in address units of 16 B
-                        ptx::mma_i8(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    }
-                    ptx::mma_commit(ptx::smem_addr(&empty_bar[stage])); // frees the smem slot when these MMAs retire
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                    for (uint32_t k = 1; k < BK / UMMA_K; ++k) // +32 bytes of K = +2 in descriptor address units
+                        ptx::mma_i8(tmem_d, ptx::desc_from_lo(a_lo + 2u * k), ptx::desc_from_lo(b_lo + 2u * k), idesc, 1u);
+                    ptx::mma_commit(empty0 + stage * 8u); // frees the smem slot when these MMAs retire
+                    stage = nstage; phase = nphase;
                 }
                 if (ok) ptx::mma_commit(ptx::smem_addr(&acc_full_bar[buf]));
             }
@@ -395,6 +404,9 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
+            long long t_wait = 0;
+            const long long t_begin = clock64();
+            const uint32_t full_local0 = ptx::smem_addr(&full_bar[0]), full_leader0 = ptx::map_to_cta(full_local0, 0);
             for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
                 const int m_tile = tile % p.num_m_tiles;
                 const int n_tile = tile / p.num_m_tiles;
@@ -404,55 +416,70 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                 const int row_b = p.mode == EPI_SWIGLU_F16 ? n_tile * C::HALF_N + (int)rank * p.act_dim
                                                            : n_tile * C::BN + (int)rank * C::HALF_N;
                 for (int kb = 0; kb < nkb; ++kb) {
+                    const long long tw = p.stall ? clock64() : 0;
                     if (!ptx::mbar_wait(ptx::smem_addr(&empty_bar[stage]), phase ^ 1u, p.status, ST_PRODUCER_TIMEOUT)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t full_local = ptx::smem_addr(&full_bar[stage]);
-                    const uint32_t full_leader = ptx::map_to_cta(full_local, 0);
+                    if (p.stall) t_wait += clock64() - tw;
                     const uint32_t sa = ring + stage * C::STAGE_BYTES;
-                    if (leader) ptx::mbar_arrive_expect_tx(full_local, 2 * C::STAGE_BYTES);
-                    ptx::tma_load_2d_pair(sa, &tmap_a, full_leader, kb * BK, row_a);
-                    ptx::tma_load_2d_pair(sa + C::A_BYTES, &tmap_b, full_leader, kb * BK, row_b);
+                    if (leader) ptx::mbar_arrive_expect_tx(full_local0 + stage * 8u, 2 * C::STAGE_BYTES);
+                    ptx::tma_load_2d_pair(sa, &tmap_a, full_leader0 + stage * 8u, kb * BK, row_a);
+                    ptx::tma_load_2d_pair(sa + C::A_BYTES, &tmap_b, full_leader0 + stage * 8u, kb * BK, row_b);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
+            }
+            if (p.stall) {
+                p.stall[blockIdx.x * 8 + 3] = (unsigned long long)t_wait;
+                p.stall[blockIdx.x * 8 + 4] = (unsigned long long)(clock64() - t_begin);
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (leader CTA only)
         if (lane == 0 && leader) {
             constexpr uint32_t idesc = ptx::make_i8_idesc(256, C::BN);
+            const uint32_t a_lo0 = ptx::desc_lo_sw128(ring), full0 = ptx::smem_addr(&full_bar[0]), empty0 = ptx::smem_addr(&empty_bar[0]);
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int it = 0;
+            bool ready = false;
+            long long t_full = 0, t_acc = 0;
+            const long long t_begin = clock64();
             for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
                 const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+                const long long ta = p.stall ? clock64() : 0;
                 if (!ptx::mbar_wait(ptx::smem_addr(&acc_empty_bar[buf]), acc_phase ^ 1u, p.status, ST_MMA_ACC_TIMEOUT)) break;
+                if (p.stall) t_acc += clock64() - ta;
                 ptx::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * C::BN;
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!ptx::mbar_wait(ptx::smem_addr(&full_bar[stage]), phase, p.status, ST_MMA_FULL_TIMEOUT)) {
-                        ok = false;
-                        break;
+                    if (!ready) { // the poll issued one iteration ago found the stage still empty: wait for it
+                        const long long tw = p.stall ? clock64() : 0;
+                        if (!ptx::mbar_wait(full0 + stage * 8u, phase, p.status, ST_MMA_FULL_TIMEOUT)) {
+                            ok = false;
+                            break;
+                        }
+                        if (p.stall) t_full += clock64() - tw;
                     }
                     ptx::tc_fence_after();
-                    const uint32_t sa = ring + stage * C::STAGE_BYTES;
-                    const uint64_t adesc = ptx::make_kmajor_sw128_desc(sa);
-                    const uint64_t bdesc = ptx::make_kmajor_sw128_desc(sa + C::A_BYTES);
+                    uint32_t nstage = stage + 1, nphase = phase;
+                    if (nstage == C::STAGES) { nstage = 0; nphase ^= 1u; }
+                    ready = ptx::mbar_try_wait(full0 + nstage * 8u, nphase); // used in the next iteration
+                    const uint32_t a_lo = a_lo0 + stage * (uint32_t)(C::STAGE_BYTES >> 4), b_lo = a_lo + (uint32_t)(C::A_BYTES >> 4);
+                    ptx::mma_i8_pair(tmem_d, ptx::desc_from_lo(a_lo), ptx::desc_from_lo(b_lo), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        ptx::mma_i8_pair(tmem_d, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    // free the slot in both CTAs once these MMAs retire
-                    const uint32_t empty_local = ptx::smem_addr(&empty_bar[stage]);
-                    ptx::mma_commit_pair(empty_local);
-                    ptx::mma_commit_pair(ptx::map_to_cta(empty_local, 1));
-                    if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+                    for (uint32_t k = 1; k < BK / UMMA_K; ++k)
+                        ptx::mma_i8_pair(tmem_d, ptx::desc_from_lo(a_lo + 2u * k), ptx::desc_from_lo(b_lo + 2u * k), idesc, 1u);
+                    // one commit frees the slot in both CTAs once these MMAs retire (a signal multicast, not a load)
+                    ptx::mma_commit_pair_mcast(empty0 + stage * 8u, 3);
+                    stage = nstage; phase = nphase;
                 }
-                if (ok) {
-                    const uint32_t accf = ptx::smem_addr(&acc_full_bar[buf]);
-                    ptx::mma_commit_pair(accf);
-                    ptx::mma_commit_pair(ptx::map_to_cta(accf, 1));
-                }
+                if (ok) ptx::mma_commit_pair_mcast(ptx::smem_addr(&acc_full_bar[buf]), 3);
+            }
+            if (p.stall) {
+                p.stall[blockIdx.x * 8 + 0] = (unsigned long long)(clock64() - t_begin);
+                p.stall[blockIdx.x * 8 + 1] = (unsigned long long)t_full;
+                p.stall[blockIdx.x * 8 + 2] = (unsigned long long)t_acc;
             }
         }
     } else {
@@ -463,11 +490,15 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         uint32_t sel = 0;
         if (EW == 4 && lane == 0 && p.mode != EPI_PUSH_I32) ptx::prefetch_tensormap(&tmap_out);
         int it = 0;
+        long long t_accfull = 0;
+        const long long t_begin = clock64();
         for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
             const int m_tile = tile % p.num_m_tiles;
             const int n_tile = tile / p.num_m_tiles;
             const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
+            const long long tw = p.stall ? clock64() : 0;
             if (!ptx::mbar_wait(ptx::smem_addr(&acc_full_bar[buf]), acc_phase, p.status, ST_EPI_TIMEOUT)) break;
+            if (p.stall) t_accfull += clock64() - tw;
             ptx::tc_fence_after();
 
             const int row = m_tile * 256 + (int)rank * BM + quarter * 32 + lane;
@@ -570,6 +601,10 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
         }
         if (EW == 4 && lane == 0) ptx::bulk_wait_group<0>(); // the staging buffers must outlive the stores that read them
+        if (p.stall && warp == 2 && lane == 0) {
+            p.stall[blockIdx.x * 8 + 5] = (unsigned long long)t_accfull;
+            p.stall[blockIdx.x * 8 + 6] = (unsigned long long)(clock64() - t_begin);
+        }
     }
 
     // Neither CTA may leave while its partner can still read its shared memory or signal its barriers.
@@ -627,7 +662,12 @@ bool make_output_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Diagnostics switch (pplb200_debug_gemm_stall_counters): device array the CTA-pair kernel fills when non-null.
+unsigned long long* g_stall_counters = nullptr;
+
 void fill_common(KernelParams& p, const GemmArgs& a, unsigned int* status) {
+    p.stall = g_stall_counters;
+    { const char* e = getenv("PPLB200_EXP"); p.exp_flags = e ? atoi(e) : 0; }
     p.M = (int32_t)a.M; p.N = (int32_t)a.N;
     p.num_k_blocks = (int32_t)((a.K + BK - 1) / BK);
     p.mode = a.mode;
@@ -761,6 +801,8 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     if (m_tiles * ((a.N + 127) / 128) >= dev->sms) return launch_bn<128>(stream, a, *dev);
     return launch_bn<64>(stream, a, *dev);
 }
+
+void set_stall_counters(void* dev_ptr) { g_stall_counters = static_cast<unsigned long long*>(dev_ptr); }
 
 int32_t gemm_status(int32_t reset) {
     const DeviceInfo* dev = device_info();

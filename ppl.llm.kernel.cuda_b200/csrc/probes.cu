@@ -24,7 +24,7 @@ struct ProbeResult { // one per launch, written by CTA 0
     unsigned long long cycles; // SM cycles between first issue and completion
     unsigned long long nanos;  // globaltimer over the same span
     unsigned int status;
-    unsigned int pad;
+    unsigned int copies;       // tensor_peak with loads: 32 KiB copies CTA 0 completed while the MMAs ran
 };
 
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
@@ -39,11 +39,25 @@ __device__ __forceinline__ uint32_t hash32(uint32_t x) {
 }
 
 // PAIR = false: one CTA per SM, M 128 x N 256.  PAIR = true: clusters of two, cta_group::2, M 256 x N 256.
+// With stream_src != nullptr a second thread keeps `LOAD_STAGES` bulk copies of 32 KiB from global memory in flight into
+// spare shared memory for as long as the MMAs run (nothing consumes them): the tensor cores then read their operands
+// while the copy engine fills shared memory at the rate a real GEMM main loop does.
+constexpr int LOAD_STAGES = 5;
+constexpr int LOAD_BYTES = 32 * 1024;
+
+__device__ __forceinline__ void probe_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
 template <bool PAIR>
 __global__ void __launch_bounds__(128, 1)
-tensor_peak_kernel(int mmas, ProbeResult* result) {
+tensor_peak_kernel(int mmas, int commit_pattern, ProbeResult* result, const uint8_t* stream_src, long long stream_chunks) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t done_bar;
+    __shared__ __align__(8) uint64_t load_bar[LOAD_STAGES];
+    __shared__ __align__(8) uint64_t slot_bar; // target of the periodic commits (nobody waits on it)
+    __shared__ volatile int mma_done;
     __shared__ uint32_t tmem_base_slot;
     constexpr int A_BYTES = 128 * PROBE_BK;
     constexpr int B_BYTES = (PAIR ? 128 : 256) * PROBE_BK;
@@ -58,6 +72,9 @@ tensor_peak_kernel(int mmas, ProbeResult* result) {
         words[i] = hash32(i * 2654435761u + blockIdx.x * 40503u + 12345u);
     if (threadIdx.x == 0) {
         ptx::mbar_init(ptx::smem_addr(&done_bar), 1);
+        for (int i = 0; i < LOAD_STAGES; ++i) ptx::mbar_init(ptx::smem_addr(&load_bar[i]), 1);
+        ptx::mbar_init(ptx::smem_addr(&slot_bar), 1);
+        mma_done = 0;
         ptx::fence_mbar_init();
     }
     if (warp == 1) {
@@ -75,10 +92,23 @@ tensor_peak_kernel(int mmas, ProbeResult* result) {
         const uint64_t adesc = ptx::make_kmajor_sw128_desc(ring);
         const uint64_t bdesc = ptx::make_kmajor_sw128_desc(ring + A_BYTES);
         const unsigned long long c0 = clock64(), n0 = globaltimer_ns();
+        // commit_pattern: bits 0-7 = commit to a barrier after every that many MMAs (0: never), as a GEMM main
+        // loop does to release an operand slot; bit 8 = a second commit to the partner CTA's barrier;
+        // bit 9 = one multicast commit to both CTAs instead
+        const int every = commit_pattern & 255;
+        const uint32_t slot = ptx::smem_addr(&slot_bar);
         for (int i = 0; i < mmas; ++i) {
             const uint32_t k = (uint32_t)i & 3u;
             if (PAIR) ptx::mma_i8_pair(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, i != 0 ? 1u : 0u);
             else ptx::mma_i8(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, i != 0 ? 1u : 0u);
+            if (every != 0 && (i + 1) % every == 0) {
+                if (!PAIR) ptx::mma_commit(slot);
+                else if (commit_pattern & 512) ptx::mma_commit_pair_mcast(slot, 3);
+                else {
+                    ptx::mma_commit_pair(slot);
+                    if (commit_pattern & 256) ptx::mma_commit_pair(ptx::map_to_cta(slot, 1));
+                }
+            }
         }
         if (PAIR) ptx::mma_commit_pair(ptx::smem_addr(&done_bar)); else ptx::mma_commit(ptx::smem_addr(&done_bar));
         ptx::mbar_wait(ptx::smem_addr(&done_bar), 0, &result->status, ST_PROBE_TIMEOUT);
@@ -87,6 +117,39 @@ tensor_peak_kernel(int mmas, ProbeResult* result) {
             result->cycles = c1 - c0;
             result->nanos = n1 - n0;
         }
+        mma_done = 1;
+    } else if (threadIdx.x == 64 && stream_src != nullptr && stream_chunks > 0) {
+        // loader: LOAD_STAGES copies in flight until the MMA thread of this CTA (of the leader: see below) is done
+        const uint32_t spare = ring + 64 * 1024; // past the operand tiles
+        long long c = blockIdx.x % stream_chunks;
+        uint32_t parity = 0;
+        for (int i = 0; i < LOAD_STAGES; ++i) {
+            const uint32_t bar = ptx::smem_addr(&load_bar[i]);
+            ptx::mbar_arrive_expect_tx(bar, LOAD_BYTES);
+            probe_bulk_load(spare + i * LOAD_BYTES, stream_src + c * LOAD_BYTES, LOAD_BYTES, bar);
+            c = (c + gridDim.x) % stream_chunks;
+        }
+        // both CTAs of a pair watch the leader's flag (the follower through distributed shared memory)
+        const uint32_t flag = ptx::map_to_cta(ptx::smem_addr(const_cast<int*>(&mma_done)), 0);
+        unsigned long long copies = 0;
+        for (bool stop = false; !stop;) {
+            for (int i = 0; i < LOAD_STAGES && !stop; ++i) {
+                const uint32_t bar = ptx::smem_addr(&load_bar[i]);
+                if (!ptx::mbar_wait(bar, parity, &result->status, ST_PROBE_TIMEOUT)) { stop = true; break; }
+                ptx::mbar_arrive_expect_tx(bar, LOAD_BYTES);
+                probe_bulk_load(spare + i * LOAD_BYTES, stream_src + c * LOAD_BYTES, LOAD_BYTES, bar);
+                c = (c + gridDim.x) % stream_chunks;
+                ++copies;
+            }
+            parity ^= 1u;
+            int done;
+            if (PAIR) asm volatile("ld.volatile.shared::cluster.s32 %0, [%1];" : "=r"(done) : "r"(flag) : "memory");
+            else done = mma_done;
+            if (done || copies > (1ull << 26)) stop = true;
+        }
+        if (blockIdx.x == 0) result->copies = (unsigned int)copies;
+        for (int i = 0; i < LOAD_STAGES; ++i) // drain: no copy may be in flight when the CTA exits
+            ptx::mbar_wait(ptx::smem_addr(&load_bar[i]), parity, &result->status, ST_PROBE_TIMEOUT);
     }
     ptx::tc_fence_before();
     if (PAIR) ptx::cluster_sync_all(); else __syncthreads();
@@ -140,15 +203,19 @@ using namespace pplb200;
 
 extern "C" {
 
-int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream_, int32_t cta_pairs, int32_t mmas_per_cta, void* result24) {
+int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream_, int32_t cta_pairs, int32_t mmas_per_cta, int32_t commit_pattern, const void* stream_src,
+                                  int64_t stream_bytes, void* result24) {
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!result24 || mmas_per_cta < 1 || mmas_per_cta > (1 << 22)) return fail(RC_INVALID_VALUE, "bad probe arguments");
+    if (stream_src && (!aligned16(stream_src) || stream_bytes < LOAD_BYTES)) return fail(RC_INVALID_VALUE, "bad stream source");
+    const uint8_t* src = (const uint8_t*)stream_src;
+    const long long chunks = stream_src ? stream_bytes / LOAD_BYTES : 0;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return fail(RC_DEVICE_RUNTIME_ERROR, "device query failed");
     ProbeResult* res = (ProbeResult*)result24;
     if (cudaMemsetAsync(res, 0, sizeof(ProbeResult), stream) != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
-    const int smem = 128 * 1024; // operands use 32 / 48 KiB; more than half of an SM's shared memory keeps it to one CTA per SM
+    const int smem = 226 * 1024; // operands 32 / 48 KiB, spare area for the optional loads from 64 KiB up: one CTA per SM
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(128, 1, 1);
     cfg.dynamicSmemBytes = smem;
@@ -162,12 +229,12 @@ int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream_, int32_t cta_pairs, i
             return fail(RC_DEVICE_RUNTIME_ERROR, "shared-memory opt-in failed");
         cfg.gridDim = dim3((unsigned)(sms / 2 * 2), 1, 1);
         cfg.attrs = &attr; cfg.numAttrs = 1;
-        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<true>, (int)mmas_per_cta, res);
+        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<true>, (int)mmas_per_cta, (int)commit_pattern, res, src, chunks);
     } else {
         if (cudaFuncSetAttribute(tensor_peak_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return fail(RC_DEVICE_RUNTIME_ERROR, "shared-memory opt-in failed");
         cfg.gridDim = dim3((unsigned)sms, 1, 1);
-        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<false>, (int)mmas_per_cta, res);
+        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<false>, (int)mmas_per_cta, (int)commit_pattern, res, src, chunks);
     }
     if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "probe launch failed: %s", cudaGetErrorString(e));
     return RC_SUCCESS;

@@ -107,6 +107,12 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// Asks the TMA unit to bring the box at (x, y) into L2 (no shared-memory destination, no completion signal).
+__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y) : "memory");
+}
+
 // ---- tcgen05 / TMEM ---------------------------------------------------------------------------
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) { // whole warp
@@ -208,6 +214,13 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar_cluster_addr) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
+// One commit that arrives on the mbarrier at the same shared-memory offset in every CTA of `cta_mask` (bit i =
+// cluster rank i).  This is a signal multicast, not a data load.
+__device__ __forceinline__ void mma_commit_pair_mcast(uint32_t bar_local_addr, uint16_t cta_mask) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar_local_addr), "h"(cta_mask) : "memory");
+}
+
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes with the
 // 128-byte swizzle (what a TMA box {128 B, rows} with CU_TENSOR_MAP_SWIZZLE_128B produces):
 // start address >> 4 in bits [0,14); leading-dimension offset (unused for swizzled K-major) = 1
@@ -220,6 +233,18 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_byte_ad
     d |= (uint64_t)(1024 >> 4) << 32;
     d |= (uint64_t)1 << 46;
     d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// The same descriptor split for the issue loop: the high word is a constant, the low word is
+// (address >> 4) | 1 << 16, so stepping through stages and K sub-blocks is one 32-bit add.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t smem_byte_addr) {
+    return ((smem_byte_addr & 0x3ffffu) >> 4) | (1u << 16);
+}
+__device__ __forceinline__ uint64_t desc_from_lo(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(kDescHiSw128));
     return d;
 }
 

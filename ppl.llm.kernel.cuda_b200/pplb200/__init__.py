@@ -41,7 +41,7 @@ EXPORTS = [
     "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
     "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
     "pplb200_i8i8_minmax_quantize_fp16_p2p",
-    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32",
+    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -90,7 +90,9 @@ def _load():
     lib.pplb200_i8i8_row_parallel_linear_p2p.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32, vp]
     lib.pplb200_i8i8_minmax_quantize_fp16_p2p.argtypes = [vp, vp, vp, i64, i64, f32, i32, vp, vp]
     lib.pplb200_i8i8_gemm_i32.argtypes = [vp, vp, i64, vp, i64, i64, i64, i64, i32, i32, vp, vp, i64]
-    lib.pplb200_probe_tensor_peak.argtypes = [vp, i32, i32, vp]
+    lib.pplb200_probe_tensor_peak.argtypes = [vp, i32, i32, i32, vp, i64, vp]
+    lib.pplb200_debug_gemm_stall_counters.argtypes = [vp]
+    lib.pplb200_debug_gemm_stall_counters.restype = None
     lib.pplb200_probe_stream_read.argtypes = [vp, vp, i64, vp]
     lib.pplb200_nccl_get_unique_id.argtypes = [vp]
     lib.pplb200_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
@@ -100,7 +102,7 @@ def _load():
     lib.pplb200_layout_offset.restype = i64
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if fn.restype is ctypes.c_int:
+        if name != "pplb200_debug_gemm_stall_counters" and fn.restype is ctypes.c_int:
             fn.restype = i32
     return lib
 
@@ -436,53 +438,94 @@ def minmax_quantize_fp16_p2p(p2p, x_shard, up_scale=TOKEN_UP_SCALE, out=None, sc
 
 def _probe_record(t):
     import struct
-    cycles, nanos, status, _ = struct.unpack("<QQII", bytes(t.cpu().numpy().tobytes()))
-    return cycles, nanos, status
+    cycles, nanos, status, copies = struct.unpack("<QQII", bytes(t.cpu().numpy().tobytes()))
+    return cycles, nanos, status, copies
 
 
-def tensor_peak_probe(mmas_per_cta=8192, sustained_launches=100):
-    """int8 tcgen05 issue-rate ceiling of the current device: all SMs issue kind::i8 MMAs on operands that stay
-    in shared memory.  "tops" is the best single launch of the CTA-pair form (the shape the prefill GEMM uses);
-    "sustained_tops" the rate over `sustained_launches` launches back to back (tens of milliseconds, long
-    enough for the power limit to pull the clock down)."""
+def _peak_case(pairs, mmas_per_cta, src, launches, commit_pattern=0):
+    """(best single-launch TOP/s, SM MHz of that launch, TOP/s over `launches` back-to-back launches, its SM MHz,
+    32 KiB copies CTA 0 made per launch)."""
     import torch
     rec = torch.zeros((24,), dtype=torch.uint8, device="cuda")
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-    out = {}
-    for pairs in (0, 1):
-        ctas = sms if not pairs else sms // 2
-        ops = 2.0 * (256 if pairs else 128) * 256 * 32 * mmas_per_cta * ctas
-        best, mhz = None, None
-        _check(lib.pplb200_probe_tensor_peak(_stream(), pairs, mmas_per_cta, _ptr(rec)))  # warm-up, module load
-        for _ in range(5):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            _check(lib.pplb200_probe_tensor_peak(_stream(), pairs, mmas_per_cta, _ptr(rec)))
-            e1.record()
-            torch.cuda.synchronize()
-            cycles, nanos, status = _probe_record(rec)
-            if status:
-                raise RuntimeError("tensor peak probe: a bounded wait gave up")
-            ms = e0.elapsed_time(e1)
-            if best is None or ms < best:
-                best, mhz = ms, cycles / max(nanos, 1) * 1e3
+    ctas = sms // 2 if pairs else sms
+    ops = 2.0 * (256 if pairs else 128) * 256 * 32 * mmas_per_cta * ctas
+    sp, sb = (None, 0) if src is None else (_ptr(src), src.numel())
+
+    def launch():
+        _check(lib.pplb200_probe_tensor_peak(_stream(), pairs, mmas_per_cta, commit_pattern, sp, sb, _ptr(rec)))
+
+    launch()  # warm-up, module load
+    best, mhz, copies = None, None, 0
+    for _ in range(5):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(sustained_launches):
-            _check(lib.pplb200_probe_tensor_peak(_stream(), pairs, mmas_per_cta, _ptr(rec)))
+        launch()
         e1.record()
         torch.cuda.synchronize()
-        cycles, nanos, _ = _probe_record(rec)
-        sus = e0.elapsed_time(e1) / sustained_launches
-        key = "pair" if pairs else "single"
-        out[key] = {"tops": ops / (best * 1e-3) / 1e12, "launch_ms": best, "sm_mhz": round(mhz, 1),
-                    "sustained_tops": ops / (sus * 1e-3) / 1e12, "sustained_sm_mhz": round(cycles / max(nanos, 1) * 1e3, 1)}
-    top = max(out["pair"]["tops"], out["single"]["tops"])
-    return {"tops": top, "sustained_tops": max(out["pair"]["sustained_tops"], out["single"]["sustained_tops"]),
-            "how": "tcgen05.mma kind::i8, operands resident in shared memory, no loads; %d MMAs per CTA, all SMs; "
-                   "best of 5 launches, SM clock read inside the kernel; sustained = %d launches back to back"
-                   % (mmas_per_cta, sustained_launches),
-            "cta_group_2_m256_n256": out["pair"], "cta_group_1_m128_n256": out["single"]}
+        cycles, nanos, status, cp = _probe_record(rec)
+        if status:
+            raise RuntimeError("tensor peak probe: a bounded wait gave up")
+        ms = e0.elapsed_time(e1)
+        if best is None or ms < best:
+            best, mhz, copies = ms, cycles / max(nanos, 1) * 1e3, cp
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(launches):
+        launch()
+    e1.record()
+    torch.cuda.synchronize()
+    cycles, nanos, _, _ = _probe_record(rec)
+    sus = e0.elapsed_time(e1) / launches
+    d = {"tops": round(ops / (best * 1e-3) / 1e12, 1), "launch_ms": round(best, 4), "sm_mhz": round(mhz, 1),
+         "sustained_tops": round(ops / (sus * 1e-3) / 1e12, 1), "sustained_sm_mhz": round(cycles / max(nanos, 1) * 1e3, 1)}
+    if src is not None:
+        d["fill_gb_per_s_per_sm"] = round(copies * 32768 / (best * 1e-3) / 1e9, 1)
+    return d
+
+
+def tensor_peak_probe(mmas_per_cta=8192, sustained_launches=100, with_loads=True):
+    """int8 tcgen05 issue-rate ceiling of the current device: all SMs issue kind::i8 MMAs on operands that stay
+    in shared memory.  "tops" is the best single launch over the two MMA shapes; "sustained_tops" the rate over
+    `sustained_launches` launches back to back (tens of milliseconds, long enough for the power limit to pull the
+    clock down).  with_loads adds the same measurement while every SM also streams bulk copies from global memory
+    into spare shared memory (what a GEMM main loop does to the shared-memory ports and to the power budget)."""
+    import torch
+    out = {"cta_group_1_m128_n256": _peak_case(0, mmas_per_cta, None, sustained_launches),
+           "cta_group_2_m256_n256": _peak_case(1, mmas_per_cta, None, sustained_launches)}
+    if with_loads:
+        pool = torch.randint(0, 255, (24 << 20,), dtype=torch.uint8, device="cuda")  # stays in L2, as a GEMM's operands mostly do
+        out["cta_group_2_m256_n256_with_loads"] = _peak_case(1, mmas_per_cta, pool, sustained_launches)
+        del pool
+    no_load = [out["cta_group_1_m128_n256"], out["cta_group_2_m256_n256"]]
+    return dict(out, tops=max(c["tops"] for c in no_load), sustained_tops=max(c["sustained_tops"] for c in no_load),
+                how="tcgen05.mma kind::i8, operands resident in shared memory, no loads; %d MMAs per CTA, all SMs; best of 5 "
+                    "launches, SM clock read inside the kernel; sustained = %d launches back to back"
+                    % (mmas_per_cta, sustained_launches))
+
+
+def gemm_stall_profile(fn):
+    """Runs fn() (which launches the CTA-pair GEMM) with the kernel's wait counters switched on and returns
+    their means over the CTAs as fractions of the thread's run time."""
+    import torch
+    buf = torch.zeros((296 * 8,), dtype=torch.int64, device="cuda")
+    lib.pplb200_debug_gemm_stall_counters(_ptr(buf))
+    try:
+        fn()
+        torch.cuda.synchronize()
+    finally:
+        lib.pplb200_debug_gemm_stall_counters(None)
+    c = buf.view(296, 8).double().cpu().numpy()
+    lead = c[c[:, 0] > 0]      # leader CTAs carry the MMA thread
+    prod = c[c[:, 4] > 0]
+    epi = c[c[:, 6] > 0]
+    if len(lead) == 0:
+        return None
+    return {"mma_thread_cycles": float(lead[:, 0].mean()),
+            "mma_waits_for_operands": float((lead[:, 1] / lead[:, 0]).mean()),
+            "mma_waits_for_accumulator": float((lead[:, 2] / lead[:, 0]).mean()),
+            "tma_thread_waits_for_slot": float((prod[:, 3] / prod[:, 4]).mean()),
+            "epilogue_waits_for_accumulator": float((epi[:, 5] / epi[:, 6]).mean())}
 
 
 def stream_read_probe(sizes=(16 << 20, 48 << 20, 384 << 20), pool_bytes=1536 << 20, reps=12):
