@@ -212,6 +212,14 @@ int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const v
  * gather_output != 0: fp16; size == 1 -> output [M,N]; size > 1 -> all-gather into gather_buffer
  *   [size, M, N/size] then transpose to output [M, N].  quant_buffer is unused (the int32
  *   accumulators never leave the chip) but accepted.
+ * weight_layout ROW_MAJOR: operands as above.  COL32_2R_4R4 / COL4_4R2_8C (the Turing / Ampere tensor-core orders
+ *   the reference hands to gemm_i8i8i32_col32, src/.../pmx/i8i8/column_parallel_linear.cu:66-75,120-131): `input`
+ *   is then COL32 [M, K], the weight is in that order, and with gather_output == 0 the raw int32 output is COL32
+ *   [M, N/size], exactly as the reference leaves them.  sm_100a's tensor cores read none of these orders, so both
+ *   operands are first re-laid out into `ws`, which must then hold
+ *   roundup(M*K, 256) + roundup(N/size*K, 256) (+ roundup(M*N/size*4, 256) when gather_output == 0) bytes, 256-byte
+ *   aligned (RC_UNSUPPORTED with the needed size in pplb200_last_error otherwise); K % 32 == 0, (N/size) % 32 == 0.
+ *   Converting the weights once at load time with pplb200_i8i8_relayout and passing ROW_MAJOR avoids that pass.
  */
 int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream, const void* input, int64_t M,
                                             const void* weight, const void* optional_bias,
@@ -233,6 +241,8 @@ int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream, const void*
  *   the full-row scale_M and the same bias.
  * reduce_mode 1 (reference order): dequantize each partial to fp16, bias on rank 0 only, then fp16
  *   all-reduce (src/.../pmx/i8i8/row_parallel_linear.cu:84,131-158).
+ * weight_layout: as for the column-parallel linear (COL32 input shard [M, K/size], legacy weight shard, operands
+ *   re-laid out into `ws` of roundup(M*K/size, 256) + roundup(N*K/size, 256) bytes).
  */
 int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream, const void* input, int64_t M, int64_t input_ld,
                                          const void* weight, const void* optional_bias,
@@ -333,6 +343,17 @@ int32_t pplb200_i8i8_gemm_status(int32_t reset);
  * an accumulator, [6] that warp ran.  NULL switches the recording off again.
  */
 void pplb200_debug_gemm_stall_counters(void* counters);
+
+/*
+ * Storage-order change of a [rows, cols] matrix of int8 (elem_bytes 1) or int32 (elem_bytes 4) elements between
+ * any two of ROW_MAJOR, COL32, COL32_2R_4R4 and COL4_4R2_8C (index maps of
+ * include/ppl/kernel/llm/cuda/common/matrix_layout.h:34-142; no counterpart function in the reference, whose
+ * callers prepare such weights offline).  Meant for load time: weights stored for the Turing / Ampere kernels
+ * -> ROW_MAJOR once, instead of on every call of a linear.  src != dst; cols % 32 == 0 when a tiled order is
+ * involved (cols % 4 otherwise); rows % 32 == 0 for COL32_2R_4R4, rows % 8 == 0 for COL4_4R2_8C.
+ */
+int32_t pplb200_i8i8_relayout(pplb200_stream_t stream, const void* src, int32_t src_layout, void* dst, int32_t dst_layout,
+                              int64_t rows, int64_t cols, int32_t elem_bytes);
 
 /*
  * Measurement probes (no counterpart in the reference; they give the roofline denominators that

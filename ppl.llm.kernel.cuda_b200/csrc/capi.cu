@@ -315,6 +315,23 @@ int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const v
                       down_scale_N, requant_up_scale, gws, gemm_ws_bytes(M, epilogue_mode), y, N, y_q, y_q_scale, true);
 }
 
+int32_t pplb200_i8i8_relayout(pplb200_stream_t stream, const void* src, int32_t src_layout, void* dst, int32_t dst_layout,
+                              int64_t rows, int64_t cols, int32_t elem_bytes) {
+    auto known = [](int32_t l) { return l == LAYOUT_ROW_MAJOR || l == LAYOUT_COL32 || l == LAYOUT_COL32_2R_4R4 || l == LAYOUT_COL4_4R2_8C; };
+    if (!known(src_layout) || !known(dst_layout)) return fail(RC_UNSUPPORTED, "unsupported matrix layout: %d -> %d", src_layout, dst_layout);
+    if (elem_bytes != 1 && elem_bytes != 4) return fail(RC_UNSUPPORTED, "element size must be 1 (int8) or 4 (int32)");
+    if (rows < 0 || cols < 0) return fail(RC_INVALID_VALUE, "negative extent");
+    if (rows == 0 || cols == 0) return RC_SUCCESS;
+    if (!src || !dst || src == dst) return fail(RC_INVALID_VALUE, "src / dst must be distinct non-null pointers");
+    const bool tiled = src_layout != LAYOUT_ROW_MAJOR || dst_layout != LAYOUT_ROW_MAJOR;
+    if (cols % 4 || (tiled && cols % 32)) return fail(RC_INVALID_VALUE, "cols must be a multiple of 32 for the tiled layouts (4 otherwise)");
+    auto rows_ok = [&](int32_t l) { return l == LAYOUT_COL32_2R_4R4 ? rows % 32 == 0 : l == LAYOUT_COL4_4R2_8C ? rows % 8 == 0 : true; };
+    if (!rows_ok(src_layout) || !rows_ok(dst_layout)) return fail(RC_INVALID_VALUE, "rows must be a multiple of 32 (COL32_2R_4R4) / 8 (COL4_4R2_8C)");
+    if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & (elem_bytes == 1 ? 3 : 15))
+        return fail(RC_INVALID_VALUE, "src / dst must be aligned to four elements");
+    return launch_relayout((cudaStream_t)stream, src, src_layout, dst, dst_layout, rows, cols, elem_bytes);
+}
+
 int32_t pplb200_i8i8_gemm_status(int32_t reset) { return gemm_status(reset); }
 void pplb200_debug_gemm_stall_counters(void* counters) { set_stall_counters(counters); }
 

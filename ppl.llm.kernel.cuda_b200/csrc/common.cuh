@@ -95,6 +95,11 @@ int32_t dequantize_split3(cudaStream_t stream, const void* acc, const void* bias
                           int64_t batch, int64_t dim, int64_t d0, int64_t d1, int64_t d2, float down_m, float down_n,
                           int32_t layout, void* o0, void* o1, void* o2);
 
+// storage-order change of a [rows, cols] matrix of 1- or 4-byte elements between any two of ROW_MAJOR, COL32,
+// COL32_2R_4R4, COL4_4R2_8C (cols % 4 == 0 and the layouts' own divisibility rules checked by the caller)
+int32_t launch_relayout(cudaStream_t stream, const void* src, int32_t src_layout, void* dst, int32_t dst_layout,
+                        int64_t rows, int64_t cols, int32_t elem_bytes);
+
 int32_t launch_transpose01_f16(cudaStream_t stream, const half* in, int64_t d0, int64_t d1, int64_t d2, half* out);
 
 struct GemmArgs {

@@ -196,6 +196,21 @@ transpose01_kernel(const VEC* __restrict__ in, int64_t d0, int64_t d1, int64_t d
     }
 }
 
+// Element-wise change of storage order of a [rows, cols] matrix, four consecutive columns (which every
+// layout but COL_MAJOR keeps contiguous) per item.  VEC = uint32_t for int8 elements, uint4 for int32.
+template <typename VEC>
+__global__ void __launch_bounds__(256)
+relayout4_kernel(const VEC* __restrict__ src, int32_t src_layout, VEC* __restrict__ dst, int32_t dst_layout, int64_t rows,
+                 int64_t cols) {
+    const int64_t quads_per_row = cols >> 2;
+    const int64_t total = rows * quads_per_row;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        // walk the DESTINATION in storage order where it is row-major (the common direction: legacy -> row-major)
+        const int64_t r = i / quads_per_row, c = (i - r * quads_per_row) << 2;
+        dst[layout_offset(dst_layout, rows, cols, r, c) >> 2] = src[layout_offset(src_layout, rows, cols, r, c) >> 2];
+    }
+}
+
 int grid_for(int64_t work_items, int tpb) {
     int64_t blocks = (work_items + tpb - 1) / tpb;
     const int64_t cap = 148 * 16;
@@ -269,6 +284,17 @@ int32_t launch_dequantize(cudaStream_t stream, const int32_t* acc, const half* b
             acc, bias, scale_m, scale_n, batch, dim, down_m, down_n, layout, out);
     }
     return check_launch("dequantize");
+}
+
+int32_t launch_relayout(cudaStream_t stream, const void* src, int32_t src_layout, void* dst, int32_t dst_layout,
+                        int64_t rows, int64_t cols, int32_t elem_bytes) {
+    if (rows * cols == 0) return RC_SUCCESS;
+    const int grid = grid_for(rows * (cols >> 2), 256);
+    if (elem_bytes == 1)
+        relayout4_kernel<uint32_t><<<grid, 256, 0, stream>>>((const uint32_t*)src, src_layout, (uint32_t*)dst, dst_layout, rows, cols);
+    else
+        relayout4_kernel<uint4><<<grid, 256, 0, stream>>>((const uint4*)src, src_layout, (uint4*)dst, dst_layout, rows, cols);
+    return check_launch("relayout");
 }
 
 int32_t launch_transpose01_f16(cudaStream_t stream, const half* in, int64_t d0, int64_t d1, int64_t d2, half* out) {

@@ -70,6 +70,42 @@ int32_t nccl_missing() { return fail(RC_DEVICE_RUNTIME_ERROR, "libnccl.so.2 coul
 bool weight_layout_known(int32_t l) {
     return l == LAYOUT_ROW_MAJOR || l == LAYOUT_COL4_4R2_8C || l == LAYOUT_COL32_2R_4R4;
 }
+
+// Operands in the Turing / Ampere tensor-core orders.  With such a weight layout the reference runs
+// gemm_i8i8i32_col32 (src/ppl/kernel/llm/cuda/cublas/gemm.cu:365-488): the int8 input is COL32 [M, K], the
+// weight COL32_2R_4R4 or COL4_4R2_8C [N, K], and the int32 product COL32 [M, N]
+// (pmx/i8i8/column_parallel_linear.cu:66-75,120-131).  The tensor cores of sm_100a read none of these orders, so
+// both operands are re-laid out into the caller's workspace (row-major) first; a caller that can should convert
+// its weights ONCE with pplb200_i8i8_relayout at load time and pass ROW_MAJOR instead.
+struct LegacyOperands {
+    const void* input;
+    const void* weight;
+    void* raw_tmp; // row-major int32 [M, N] scratch for the gather_output = false form
+};
+
+int64_t legacy_ws_bytes(int64_t M, int64_t N, int64_t K, bool want_raw) {
+    return round_up(M * K, 256) + round_up(N * K, 256) + (want_raw ? round_up(M * N * 4, 256) : 0);
+}
+
+int32_t prepare_legacy(cudaStream_t stream, const void* input, const void* weight, int32_t weight_layout, int64_t M, int64_t N,
+                       int64_t K, bool want_raw, void* ws, int64_t ws_bytes, LegacyOperands* out) {
+    if (K % 32 || N % 32) return fail(RC_INVALID_VALUE, "COL32 operand orders need in_features %% 32 == 0 and out_features / size %% 32 == 0");
+    const int64_t need = legacy_ws_bytes(M, N, K, want_raw);
+    if (!ws || ws_bytes < need || (reinterpret_cast<uintptr_t>(ws) & 255))
+        return fail(RC_UNSUPPORTED, "weight layout %d needs a 256-byte aligned workspace of %lld bytes to re-lay the operands out "
+                    "(got %lld); or convert the weights once with pplb200_i8i8_relayout and pass ROW_MAJOR",
+                    weight_layout, (long long)need, (long long)ws_bytes);
+    char* base = (char*)ws;
+    void* a_rm = base;
+    void* w_rm = base + round_up(M * K, 256);
+    int32_t rc = launch_relayout(stream, input, LAYOUT_COL32, a_rm, LAYOUT_ROW_MAJOR, M, K, 1);
+    if (rc != RC_SUCCESS) return rc;
+    rc = launch_relayout(stream, weight, weight_layout, w_rm, LAYOUT_ROW_MAJOR, N, K, 1);
+    if (rc != RC_SUCCESS) return rc;
+    out->input = a_rm; out->weight = w_rm;
+    out->raw_tmp = want_raw ? base + round_up(M * K, 256) + round_up(N * K, 256) : nullptr;
+    return RC_SUCCESS;
+}
 }
 
 extern "C" {
@@ -85,16 +121,28 @@ int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream_, const void
     (void)quant_buffer;
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!weight_layout_known(weight_layout)) return fail(RC_UNSUPPORTED, "unsupported weight layout:%d", weight_layout);
-    // The Turing/Ampere IMMA tile orders (COL4_4R2_8C, COL32_2R_4R4) have no tensor-core path on
-    // sm_100a; weights must be handed over row-major [N/size, K].
-    if (weight_layout != LAYOUT_ROW_MAJOR) return fail(RC_UNSUPPORTED, "weight layout %d is not available on sm_100a; use ROW_MAJOR", weight_layout);
     if (size < 1 || rank < 0 || rank >= size) return fail(RC_INVALID_VALUE, "bad rank/size %d/%d", rank, size);
     if (out_features % size) return fail(RC_INVALID_VALUE, "out_features %% size != 0");
     const int64_t Nw = out_features / size, K = in_features;
 
-    if (!gather_output) // raw int32 accumulators, no dequant (column_parallel_linear.cu:81-85,136)
-        return gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f,
-                          ws, ws_bytes, output, Nw, nullptr, nullptr);
+    LegacyOperands legacy = {};
+    if (weight_layout != LAYOUT_ROW_MAJOR) {
+        int32_t rc = prepare_legacy(stream, input, weight, weight_layout, M, Nw, K, !gather_output, ws, ws_bytes, &legacy);
+        if (rc != RC_SUCCESS) return rc;
+        input = legacy.input;
+        weight = legacy.weight;
+    }
+
+    if (!gather_output) { // raw int32 accumulators, no dequant (column_parallel_linear.cu:81-85,136)
+        if (legacy.raw_tmp == nullptr)
+            return gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f,
+                              ws, ws_bytes, output, Nw, nullptr, nullptr);
+        // legacy orders: the reference leaves the product in COL32
+        int32_t rc = gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_RAW_I32, nullptr, nullptr, nullptr, 0.f, 0.f, 0.f,
+                                nullptr, 0, legacy.raw_tmp, Nw, nullptr, nullptr);
+        if (rc != RC_SUCCESS) return rc;
+        return launch_relayout(stream, legacy.raw_tmp, LAYOUT_ROW_MAJOR, output, LAYOUT_COL32, M, Nw, 4);
+    }
 
     if (size == 1)
         return gemm_entry(stream, input, K, weight, K, M, Nw, K, EPI_DEQUANT_F16, scale_M, scale_N, optional_bias,
@@ -122,12 +170,20 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* i
     cudaStream_t stream = (cudaStream_t)stream_;
     if (!input_is_parallel) return fail(RC_UNSUPPORTED, "currently only support parallel input");
     if (!weight_layout_known(weight_layout)) return fail(RC_UNSUPPORTED, "unsupported weight layout:%d", weight_layout);
-    if (weight_layout != LAYOUT_ROW_MAJOR) return fail(RC_UNSUPPORTED, "weight layout %d is not available on sm_100a; use ROW_MAJOR", weight_layout);
     if (size < 1 || rank < 0 || rank >= size) return fail(RC_INVALID_VALUE, "bad rank/size %d/%d", rank, size);
     if (in_features % size) return fail(RC_INVALID_VALUE, "in_features %% size != 0");
     if (reduce_mode != 0 && reduce_mode != 1) return fail(RC_INVALID_VALUE, "reduce_mode must be 0 or 1");
     const int64_t N = out_features, Kw = in_features / size;
-    const int64_t lda = input_ld > 0 ? input_ld : Kw;
+    int64_t lda = input_ld > 0 ? input_ld : Kw;
+    if (weight_layout != LAYOUT_ROW_MAJOR) { // COL32 input shard, legacy weight shard: see prepare_legacy
+        if (input_ld > 0 && input_ld != Kw) return fail(RC_INVALID_VALUE, "a COL32 input has no leading dimension");
+        LegacyOperands legacy = {};
+        int32_t rc = prepare_legacy(stream, input, weight, weight_layout, M, N, Kw, false, ws, ws_bytes, &legacy);
+        if (rc != RC_SUCCESS) return rc;
+        input = legacy.input;
+        weight = legacy.weight;
+        lda = Kw;
+    }
 
     if (size == 1)
         return gemm_entry(stream, input, lda, weight, Kw, M, N, Kw, EPI_DEQUANT_F16, scale_M, scale_N, optional_bias,

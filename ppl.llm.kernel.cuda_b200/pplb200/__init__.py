@@ -41,7 +41,7 @@ EXPORTS = [
     "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
     "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
     "pplb200_i8i8_minmax_quantize_fp16_p2p",
-    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters",
+    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters", "pplb200_i8i8_relayout",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -91,6 +91,7 @@ def _load():
     lib.pplb200_i8i8_minmax_quantize_fp16_p2p.argtypes = [vp, vp, vp, i64, i64, f32, i32, vp, vp]
     lib.pplb200_i8i8_gemm_i32.argtypes = [vp, vp, i64, vp, i64, i64, i64, i64, i32, i32, vp, vp, i64]
     lib.pplb200_probe_tensor_peak.argtypes = [vp, i32, i32, i32, vp, i64, vp]
+    lib.pplb200_i8i8_relayout.argtypes = [vp, vp, i32, vp, i32, i64, i64, i32]
     lib.pplb200_debug_gemm_stall_counters.argtypes = [vp]
     lib.pplb200_debug_gemm_stall_counters.restype = None
     lib.pplb200_probe_stream_read.argtypes = [vp, vp, i64, vp]
@@ -233,6 +234,14 @@ def minmax_dequantize_fp16(acc, scale_m, scale_n, bias=None, down_m=TOKEN_DOWN_S
     return y
 
 
+def relayout(src, src_layout, dst_layout, rows, cols):
+    """Flat int8 / int32 tensor holding a [rows, cols] matrix in `src_layout` -> new flat tensor in `dst_layout`."""
+    import torch
+    dst = torch.zeros_like(src)
+    _check(lib.pplb200_i8i8_relayout(_stream(), _ptr(src), src_layout, _ptr(dst), dst_layout, rows, cols, src.element_size()))
+    return dst
+
+
 def gemm_workspace_bytes(M, N, K, mode):
     return lib.pplb200_i8i8_gemm_workspace_bytes(M, N, K, mode)
 
@@ -321,9 +330,9 @@ class W8A8Linear:
 
 def column_parallel_linear(xq, w, scale_m, scale_n, bias, in_features, out_features, rank=0, size=1, comm=None,
                            gather_output=True, gather_buffer=None, out=None, down_m=TOKEN_DOWN_SCALE,
-                           down_n=HIDDEN_DOWN_SCALE, weight_layout=MATRIX_LAYOUT_ROW_MAJOR):
+                           down_n=HIDDEN_DOWN_SCALE, weight_layout=MATRIX_LAYOUT_ROW_MAJOR, ws=None, M=None):
     import torch
-    M = xq.shape[0]
+    M = xq.shape[0] if M is None else M
     Nw = out_features // size
     if out is None:
         if gather_output:
@@ -333,23 +342,24 @@ def column_parallel_linear(xq, w, scale_m, scale_n, bias, in_features, out_featu
     _check(lib.pplb200_i8i8_column_parallel_linear(_stream(), _ptr(xq), M, _ptr(w), _ptr(bias), _ptr(scale_m),
                                                    _ptr(scale_n), down_m, down_n, in_features, out_features,
                                                    weight_layout, rank, size, comm, 1 if gather_output else 0,
-                                                   _ptr(gather_buffer), None, None, 0, _ptr(out)))
+                                                   _ptr(gather_buffer), None, _ptr(ws), 0 if ws is None else ws.numel(), _ptr(out)))
     return out
 
 
 def row_parallel_linear(xq, w, scale_m, scale_n, bias, in_features, out_features, rank=0, size=1, comm=None,
                         input_is_parallel=True, reduce_mode=0, quant_buffer=None, out=None,
-                        down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE, weight_layout=MATRIX_LAYOUT_ROW_MAJOR):
+                        down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE, weight_layout=MATRIX_LAYOUT_ROW_MAJOR, ws=None, M=None):
     import torch
-    M = xq.shape[0]
+    legacy = weight_layout != MATRIX_LAYOUT_ROW_MAJOR
+    M = (xq.shape[0] if M is None else M)
     if out is None:
         out = torch.empty((M, out_features), dtype=torch.float16, device=xq.device)
     if quant_buffer is None and size > 1 and reduce_mode == 0:
         quant_buffer = torch.empty((M, out_features), dtype=torch.int32, device=xq.device)
-    _check(lib.pplb200_i8i8_row_parallel_linear(_stream(), _ptr(xq), M, xq.stride(0), _ptr(w), _ptr(bias), _ptr(scale_m),
+    _check(lib.pplb200_i8i8_row_parallel_linear(_stream(), _ptr(xq), M, 0 if legacy else xq.stride(0), _ptr(w), _ptr(bias), _ptr(scale_m),
                                                 _ptr(scale_n), down_m, down_n, in_features, out_features,
                                                 weight_layout, rank, size, comm, 1 if input_is_parallel else 0,
-                                                reduce_mode, _ptr(quant_buffer), None, 0, _ptr(out)))
+                                                reduce_mode, _ptr(quant_buffer), _ptr(ws), 0 if ws is None else ws.numel(), _ptr(out)))
     return out
 
 

@@ -176,3 +176,28 @@ def test_reference_raw_int32_mode(cuda, oracle, ref):
     out_m = pplb200.column_parallel_linear(ta, tw, None, None, None, K, N, gather_output=False)
     assert cuda.equal(out_r, out_m)
     assert np.array_equal(out_r.cpu().numpy(), oracle.gemm(a, w))
+
+
+@pytest.mark.parametrize("use_4r4", [1, 0])
+def test_reference_col32_gemm_on_this_gpu(cuda, oracle, ref, use_4r4, capfd):
+    """The reference's gemm_i8i8i32_col32 (src/ppl/kernel/llm/cuda/cublas/gemm.cu:365-488), i.e. cuBLASLt on COL32 /
+    COL32_2R_4R4 / COL4_4R2_8C operands, called once on a small 32-aligned problem.  Either cuBLASLt runs it on this
+    GPU -- then its COL32 int32 result must equal the oracle's -- or it answers with an error code; the outcome is
+    printed (and recorded in the design notes).  This library serves those operand orders by re-laying them out."""
+    ref.ref_gemm_i8i8i32_col32.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64,
+                                           ctypes.c_int64, ctypes.c_int32, ctypes.c_void_p]
+    M, N, K = 64, 96, 128
+    rng = np.random.default_rng(5)
+    a = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    ta = _t(cuda, oracle.to_layout(a, oracle.COL32)[0])
+    tb = _t(cuda, oracle.to_layout(b, oracle.COL32_2R_4R4 if use_4r4 else oracle.COL4_4R2_8C)[0])
+    tc = cuda.zeros((M * N,), dtype=cuda.int32, device="cuda")
+    rc = ref.ref_gemm_i8i8i32_col32(ctypes.c_void_p(cuda.cuda.current_stream().cuda_stream), _p(ta), _p(tb), M, N, K, use_4r4, _p(tc))
+    cuda.cuda.synchronize()
+    print("reference gemm_i8i8i32_col32(use_4r4_kernel=%d) on %s -> RetCode %d" % (use_4r4, cuda.cuda.get_device_name(0), rc))
+    if rc == 0:
+        want = oracle.to_layout((a.astype(np.int64) @ b.astype(np.int64).T).astype(np.int32), oracle.COL32)[0]
+        assert np.array_equal(tc.cpu().numpy(), want)
+    else:
+        assert rc in (2, 10)  # RC_UNSUPPORTED / RC_DEVICE_RUNTIME_ERROR: cuBLASLt has no such kernel here
