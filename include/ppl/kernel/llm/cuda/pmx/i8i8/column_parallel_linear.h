@@ -58,6 +58,36 @@ static inline ppl::common::RetCode column_parallel_linear(
         cublas_workspace, cublas_workspace_size, output);
 }
 
+// The same operator with gather_output = true done over peer-mapped memory instead of NcclAllGather + transpose:
+// the GEMM epilogues of all ranks store their fp16 tiles straight into every rank's [M, N] matrix (see
+// pplb200_i8i8_column_parallel_linear_p2p).  `p2p_context` is a connected context of pplb200_p2p_create; it
+// replaces nccl_param, gather_buffer, quant_buffer and the cuBLAS arguments.  No counterpart in the reference.
+static inline ppl::common::RetCode column_parallel_linear(
+    const cudaStream_t stream,
+    void* p2p_context,
+    const ppl::common::TensorShape* input_shape,
+    const void* input,
+    const void* weight,
+    const ppl::common::TensorShape* bias_shape,
+    const void* bias,
+    const void* scale_M,
+    const void* scale_N,
+    const float down_scale_M,
+    const float down_scale_N,
+    const int64_t in_features,
+    const int64_t out_features,
+    void* output)
+{
+    if (bias && bias_shape->GetDataType() != ppl::common::DATATYPE_FLOAT16) {
+        LOG(ERROR) << "only support fp16 bias";
+        return ppl::common::RC_UNSUPPORTED;
+    }
+    const int64_t M = (int64_t)input_shape->CalcElementsToDimensionExcludingPadding(input_shape->GetDimCount() - 1);
+    return (ppl::common::RetCode)pplb200_i8i8_column_parallel_linear_p2p(
+        (pplb200_stream_t)stream, p2p_context, input, M, weight, bias, scale_M, scale_N, down_scale_M, down_scale_N,
+        in_features, out_features, /*phases=*/3, output);
+}
+
 }}}}}}
 
 #endif

@@ -302,6 +302,29 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream, void* ctx,
                                              int32_t phases, void* output);
 
 /*
+ * Column-parallel linear with gather_output over peer-mapped memory: what the reference does with dequantize ->
+ * ncclAllGather -> [size, M, N/size] -> [M, N] transpose (src/ppl/kernel/llm/cuda/pmx/i8i8/column_parallel_linear.cu:86-89,159-179),
+ * done by the GEMM's epilogue itself: every finished fp16 tile of this rank's [M, N/size] block is stored straight
+ * into the gathered [M, N] matrix of EVERY rank, at column offset rank * N/size, in whole 128-byte lines, while the
+ * following tiles are computed; a flag per rank then says "my block is in your area", and each rank copies the
+ * gathered matrix from its peer-mapped area into `output`.  No collective library, no transpose pass.
+ * `ctx` is a connected context of pplb200_p2p_create whose buffer holds at least
+ * pplb200_i8i8_row_parallel_p2p_bytes(M, out_features, size) bytes (the gathered matrix lives where the row-parallel
+ * operator keeps its partial sums: give the two operators separate contexts, or put a stream-level barrier across
+ * the ranks between them).  input int8 [M, in_features] (replicated), weight int8 [out_features / size, in_features],
+ * scale_N / bias this rank's slices, scale_M [M]; output fp16 [M, out_features], identical on every rank and
+ * bit-identical to the unsharded linear.  (out_features / size) % 8 == 0, in_features % 16 == 0.
+ * phases: 3 for the operation; 1 = compute and deliver, 2 = wait for the peers and copy out (lets one process that
+ * drives several ranks on one stream run "1" for every rank, then "2" for every rank).  A rank does not overwrite a
+ * peer's area before that peer has copied the previous result out (bounded wait; bits 3 and 4 of
+ * pplb200_p2p_status report a missing block / a peer that never consumed).
+ */
+int32_t pplb200_i8i8_column_parallel_linear_p2p(pplb200_stream_t stream, void* ctx, const void* input, int64_t M,
+                                                const void* weight, const void* optional_bias, const void* scale_M,
+                                                const void* scale_N, float down_scale_M, float down_scale_N,
+                                                int64_t in_features, int64_t out_features, int32_t phases, void* output);
+
+/*
  * Per-token quantizer for activations that are sharded along the quantized dimension (the input
  * of a row-parallel linear as the preceding column-parallel operator leaves it): every rank passes
  * its shard [batch, shard_dim] fp16, dense.  The row scale comes from the maximum over the WHOLE

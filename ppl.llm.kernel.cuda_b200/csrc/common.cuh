@@ -32,6 +32,7 @@ enum : int32_t {
     EPI_DEQUANT_F16_REQUANT_I8 = 2,
     EPI_SWIGLU_F16 = 3, // internal: fused gate+up projection, see pplb200_i8i8_gate_up_swiglu_requant
     EPI_PUSH_I32 = 4,   // internal: raw int32 tiles stored into the row owner's peer-mapped buffer
+    EPI_GATHER_F16 = 5, // internal: dequantized fp16 tiles stored into EVERY rank's peer-mapped [M, N_total] area
 };
 
 constexpr int kMaxPeers = 8;
@@ -121,6 +122,10 @@ struct GemmArgs {
     // push_base[owner] + ((push_rank * push_rows + r % push_rows) * ldc + col) (int32 elements).
     int32_t* push_base[kMaxPeers] = {};
     int32_t push_rows = 0, push_rank = 0;
+    // EPI_GATHER_F16: the tile's fp16 values go to ((half*)push_base[d]) + row * ldc + gather_col0 + col for every
+    // rank d < gather_ranks (ldc = width of the gathered output)
+    int32_t gather_ranks = 0;
+    int64_t gather_col0 = 0;
 };
 int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int* status, bool pdl);
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);

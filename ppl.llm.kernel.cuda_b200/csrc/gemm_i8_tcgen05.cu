@@ -59,6 +59,9 @@ struct KernelParams {
     // EPI_PUSH_I32 (CTA-pair kernel only): see GemmArgs
     int32_t* push_base[kMaxPeers];
     int32_t push_rows, push_rank;
+    // EPI_GATHER_F16 (CTA-pair kernel only): see GemmArgs
+    int32_t gather_ranks;
+    int64_t gather_col0;
 };
 
 template <int BN> struct Cfg {
@@ -102,6 +105,12 @@ __device__ __forceinline__ uint4 dequant8(const uint32_t* acc, const half* sn8, 
         if (ABSMAX) running_absmax = __hmax2(running_absmax, __habs2(h));
     }
     return ov;
+}
+
+__device__ __forceinline__ uint4 ld_shared_v4_epi(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+    return v;
 }
 
 // Epilogue staging: every epilogue warp owns two 4 KiB buffers (32 rows x 128 bytes, 128-byte swizzle) that it
@@ -488,7 +497,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         constexpr int COL_GROUPS = EW / 4;
         const int col_group = (warp - 2) >> 2;
         uint32_t sel = 0;
-        if (EW == 4 && lane == 0 && p.mode != EPI_PUSH_I32) ptx::prefetch_tensormap(&tmap_out);
+        if (EW == 4 && lane == 0 && p.mode != EPI_PUSH_I32 && p.mode != EPI_GATHER_F16) ptx::prefetch_tensormap(&tmap_out);
         int it = 0;
         long long t_accfull = 0;
         const long long t_begin = clock64();
@@ -582,6 +591,55 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                         const int r = 4 * i + sub;
                         const uint4 v = tr[r * 8 + (chunk ^ (r & 7))];
                         if (dst_row[i] != nullptr && col < p.N) *reinterpret_cast<uint4*>(dst_row[i] + col) = v;
+                    }
+                    __syncwarp();
+                }
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
+                continue;
+            }
+
+            if (EW == 4 && p.mode == EPI_GATHER_F16) {
+                // Dequantized fp16 tile, stored into the gathered [M, N_total] output of EVERY rank (this rank's own
+                // area included) at this rank's column offset.  A 32-row x 64-column slab goes through shared memory
+                // so that each store instruction writes four whole 128-byte lines, the pattern that crosses NVLink
+                // at full rate.
+                const uint32_t stage = ptx::smem_addr(epi_stage) + (uint32_t)(warp - 2) * 8192u;
+                const int row0 = m_tile * 256 + (int)rank * BM + quarter * 32;
+                const bool has_bias = p.bias != nullptr;
+                const float bscale = row_ok ? __fmul_rn(__half2float(p.scale_m[row]), p.down_m) : 0.0f;
+                const uint32_t my_row = (uint32_t)lane * 128u, sw = (uint32_t)(lane & 7);
+                const int sub = lane >> 3, chunk = lane & 7;
+                __half2 unused = __float2half2_rn(0.0f);
+#pragma unroll 1
+                for (int c0 = 0; c0 < C::BN; c0 += 64) {
+                    const int n0 = n_tile * C::BN + c0;
+                    if (n0 >= p.N) break; // warp-uniform
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const int nn = n0 + 32 * h;
+                        if (nn >= p.N) break;
+                        uint32_t acc[32];
+                        ptx::tmem_ld_32x32(taddr_row + c0 + 32 * h, acc);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            if (nn + j >= p.N) break;
+                            const uint4 v = dequant8<false>(acc + j, p.scale_n + nn + j, p.bias + nn + j, p.down_n, bscale, has_bias, unused);
+                            ptx::st_shared_v4(stage + my_row + (((uint32_t)(4 * h + (j >> 3)) ^ sw) << 4), v);
+                        }
+                    }
+                    __syncwarp();
+                    const int col = n0 + chunk * 8; // eight halves = 16 bytes per lane
+#pragma unroll 1
+                    for (int i = 0; i < 8; ++i) {
+                        const int r = 4 * i + sub;
+                        if (row0 + r >= p.M || col >= p.N) continue;
+                        const uint4 v = ld_shared_v4_epi(stage + (uint32_t)r * 128u + (((uint32_t)chunk ^ (uint32_t)(r & 7)) << 4));
+                        const int64_t off = (int64_t)(row0 + r) * p.ldc + p.gather_col0 + col;
+                        for (int d = 0; d < p.gather_ranks; ++d)
+                            *reinterpret_cast<uint4*>(reinterpret_cast<half*>(p.push_base[d]) + off) = v;
                     }
                     __syncwarp();
                 }
@@ -740,7 +798,7 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
     if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, PairCfg::HALF_N)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
     memset(&tc, 0, sizeof(tc)); // the SwiGLU and push epilogues store with their own instructions and never touch it
-    if (a.mode != EPI_SWIGLU_F16 && a.mode != EPI_PUSH_I32 &&
+    if (a.mode != EPI_SWIGLU_F16 && a.mode != EPI_PUSH_I32 && a.mode != EPI_GATHER_F16 &&
         !make_output_map(&tc, a.out, a.M, a.N, a.ldc, a.mode == EPI_RAW_I32 ? 4 : 2))
         return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (C) encode failed");
     KernelParams p{};
@@ -750,6 +808,7 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     p.act_dim = 0; p.beta = a.beta;
     for (int i = 0; i < kMaxPeers; ++i) p.push_base[i] = a.push_base[i];
     p.push_rows = a.push_rows; p.push_rank = a.push_rank;
+    p.gather_ranks = a.gather_ranks; p.gather_col0 = a.gather_col0;
     if (a.mode == EPI_SWIGLU_F16) { // a.N = 2 * act_dim weight rows; the output has act_dim columns
         p.act_dim = (int32_t)(a.N / 2);
         p.N = p.act_dim;
@@ -786,7 +845,8 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     if (a.M > INT32_MAX - BM || a.N > INT32_MAX - 256 || a.K > INT32_MAX - BK)
         return fail(RC_UNSUPPORTED, "GEMM extent beyond 2^31");
 
-    if (a.mode == EPI_SWIGLU_F16 || a.mode == EPI_PUSH_I32) return launch_pair(stream, a, *dev); // the caller checked the shape
+    if (a.mode == EPI_SWIGLU_F16 || a.mode == EPI_PUSH_I32 || a.mode == EPI_GATHER_F16)
+        return launch_pair(stream, a, *dev); // the caller checked the shape
 
     // Up to 128 tokens the op is bound by the weight stream: dedicated small-batch kernel.
     if (a.M <= 128) return launch_gemm_decode(stream, a, dev->status, a.pdl);

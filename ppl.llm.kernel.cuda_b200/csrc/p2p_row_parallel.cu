@@ -44,9 +44,12 @@ constexpr int kEpochWord = 65;          // number of produce phases enqueued so 
 constexpr long long kPeerWaitCycles = 4000000000LL;
 constexpr int kQuantEpochWord = 66;     // number of sharded-quantizer calls completed
 constexpr int kQuantDoneWord = 67;      // CTAs of the running sharded quantizer that have finished
+constexpr int kGatherEpochWord = 68;    // number of column-parallel gather operations produced so far
+constexpr int kFlagRowGathered = 4;     // flag rows of the column-parallel gather: "my block is in your area",
+constexpr int kFlagRowConsumed = 5;     // "I have copied the gathered output out of my area"
 constexpr int64_t kQuantMaxRows = 16384;
 constexpr int64_t kSlotBytes = 2 * kMaxPeers * kQuantMaxRows * 8; // [parity][source rank][row] of {epoch, max|x| bits}
-constexpr unsigned ST_WAIT_PARTIALS = 1u, ST_WAIT_ROWS = 2u, ST_WAIT_ROW_MAX = 4u;
+constexpr unsigned ST_WAIT_PARTIALS = 1u, ST_WAIT_ROWS = 2u, ST_WAIT_ROW_MAX = 4u, ST_WAIT_GATHER = 8u, ST_WAIT_CONSUMED = 16u;
 
 struct Ctx {
     int32_t rank = 0, size = 1, device = 0;
@@ -85,11 +88,11 @@ __device__ __forceinline__ uint4 ld_peer_v4(const uint4* p) {
 // the first signal of an operation advances this rank's epoch.
 // Flag rows: 2 * chunk + 0 "partial sums of column chunk `chunk` delivered", 2 * chunk + 1 "finished
 // rows of that chunk are in my staging area".
-__global__ void p2p_signal_kernel(Peers pr, int flag_row, int advance) {
+__global__ void p2p_signal_kernel(Peers pr, int flag_row, int advance, int epoch_word = kEpochWord) {
     __shared__ uint32_t epoch_s;
     const int t = threadIdx.x;
     if (t == 0) {
-        uint32_t* mine = reinterpret_cast<uint32_t*>(pr.base[pr.rank]) + kEpochWord;
+        uint32_t* mine = reinterpret_cast<uint32_t*>(pr.base[pr.rank]) + epoch_word;
         uint32_t e = *reinterpret_cast<volatile uint32_t*>(mine);
         if (advance) *reinterpret_cast<volatile uint32_t*>(mine) = ++e;
         epoch_s = e;
@@ -103,10 +106,11 @@ __global__ void p2p_signal_kernel(Peers pr, int flag_row, int advance) {
 
 // Block-wide: returns when every rank's flag of row `flag_row` has reached this rank's epoch, or when the cycle
 // budget is spent (status |= code), or at once when the status word is already set.
-__device__ __forceinline__ void wait_flags(uint32_t* flag_page, int flag_row, int size, unsigned code) {
+__device__ __forceinline__ void wait_flags(uint32_t* flag_page, int flag_row, int size, unsigned code,
+                                           int epoch_word = kEpochWord) {
     if ((int)threadIdx.x < size) {
         uint32_t* status = flag_page + kStatusWord;
-        const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(flag_page + kEpochWord);
+        const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(flag_page + epoch_word);
         const uint32_t* f = flag_page + flag_row * kMaxPeers + threadIdx.x;
         if (*reinterpret_cast<volatile uint32_t*>(status) == 0) {
             const long long t0 = clock64();
@@ -207,6 +211,22 @@ p2p_gather_kernel(Peers pr, int flag_row, int64_t staging_offset, int64_t rows, 
         for (int u = 0; u < 4; ++u)
             if (dst[u] != nullptr) *dst[u] = val[u];
     }
+}
+
+// ---- column-parallel gather ------------------------------------------------------------------
+// Before a rank may store its next block into the peers' areas, every peer must have copied the previous
+// gathered output out of its area: one warp waits (bounded) for their "consumed" flags of the previous operation.
+__global__ void p2p_wait_consumed_kernel(uint32_t* flag_page, int size) {
+    wait_flags(flag_page, kFlagRowConsumed, size, ST_WAIT_CONSUMED, kGatherEpochWord);
+}
+
+// Waits for every rank's "block delivered" flag of the current operation, then copies the gathered fp16 matrix
+// (elems halves, a multiple of 8) from this rank's area into the caller's output.
+__global__ void __launch_bounds__(256)
+p2p_gather_copy_kernel(uint32_t* flag_page, int size, const uint4* area, int64_t vecs, uint4* __restrict__ out) {
+    wait_flags(flag_page, kFlagRowGathered, size, ST_WAIT_GATHER, kGatherEpochWord);
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < vecs; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = ld_peer_v4(area + i); // written by other GPUs while this kernel was resident: never the read-only path
 }
 
 // ---- sharded per-token quantizer ------------------------------------------------------------
@@ -572,6 +592,61 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx
     if (phases & 2) reduce(stream, 0, 0, N, 8 * sms);
     if (phases & 4) gather(stream, 0, 0, N, 8 * sms);
     return check_launch("row_parallel_linear_p2p");
+}
+
+int32_t pplb200_i8i8_column_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx, const void* input, int64_t M,
+                                                const void* weight, const void* optional_bias, const void* scale_M,
+                                                const void* scale_N, float down_scale_M, float down_scale_N,
+                                                int64_t in_features, int64_t out_features, int32_t phases, void* output) {
+    clear_error();
+    cudaStream_t stream = (cudaStream_t)stream_;
+    Ctx* c = (Ctx*)ctx;
+    if (!c) return fail(RC_INVALID_VALUE, "null context");
+    if (!c->connected) return fail(RC_INVALID_VALUE, "context is not connected to its peers");
+    if (phases < 1 || phases > 3) return fail(RC_INVALID_VALUE, "phases must be a mask of 1 (produce) and 2 (finish)");
+    const int32_t size = c->size, rank = c->rank;
+    if (M < 0 || in_features <= 0 || out_features < 0) return fail(RC_INVALID_VALUE, "negative extent");
+    if (out_features % size) return fail(RC_INVALID_VALUE, "out_features %% size != 0");
+    const int64_t N = out_features, Nw = N / size, K = in_features;
+    if (Nw % 8 || K % 16) return fail(RC_UNSUPPORTED, "needs (out_features / size) %% 8 == 0 and in_features %% 16 == 0");
+    if (M > INT32_MAX / 2 || N > INT32_MAX / 2) return fail(RC_UNSUPPORTED, "extent beyond 2^30");
+    if (!input || !weight || !scale_M || !scale_N || !output) return fail(RC_INVALID_VALUE, "null pointer argument");
+    if (!aligned16(input) || !aligned16(weight) || !aligned16(output) || !aligned16(scale_N) ||
+        (optional_bias && !aligned16(optional_bias)))
+        return fail(RC_INVALID_VALUE, "operands must be 16-byte aligned");
+    const int64_t area_off = kFlagBytes + kSlotBytes;
+    if (area_off + round_up(M * N * 2, 256) > c->bytes)
+        return fail(RC_INVALID_VALUE, "peer buffer too small for a gathered output of M=%lld N=%lld", (long long)M, (long long)N);
+    if (M == 0 || N == 0) return RC_SUCCESS;
+    const Peers pr = peers_of(*c);
+    uint32_t* flag_page = reinterpret_cast<uint32_t*>(c->base);
+
+    if (phases & 1) {
+        p2p_wait_consumed_kernel<<<1, 32, 0, stream>>>(flag_page, size);
+        GemmArgs g;
+        g.A = (const int8_t*)input; g.lda = K; g.B = (const int8_t*)weight; g.ldb = K;
+        g.M = M; g.N = Nw; g.K = K; g.mode = EPI_GATHER_F16;
+        g.scale_m = (const half*)scale_M; g.scale_n = (const half*)scale_N; g.bias = (const half*)optional_bias;
+        g.down_m = down_scale_M; g.down_n = down_scale_N;
+        g.out = nullptr; g.ldc = N;
+        g.row_absmax_bits = nullptr;
+        for (int r = 0; r < size; ++r) g.push_base[r] = reinterpret_cast<int32_t*>(c->peer[r] + area_off);
+        g.gather_ranks = size; g.gather_col0 = (int64_t)rank * Nw;
+        const int32_t rc = launch_gemm(stream, g);
+        if (rc != RC_SUCCESS) return rc;
+        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, kFlagRowGathered, 1, kGatherEpochWord);
+    }
+    if (phases & 2) {
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, c->device);
+        const int64_t vecs = M * N / 8;
+        int64_t blocks = (vecs + 255) / 256;
+        if (blocks > 8 * sms) blocks = 8 * sms;
+        p2p_gather_copy_kernel<<<(unsigned)blocks, 256, 0, stream>>>(flag_page, size, reinterpret_cast<const uint4*>(c->base + area_off),
+                                                                     vecs, reinterpret_cast<uint4*>(output));
+        p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, kFlagRowConsumed, 0, kGatherEpochWord);
+    }
+    return check_launch("column_parallel_linear_p2p");
 }
 
 } // extern "C"

@@ -41,7 +41,7 @@ EXPORTS = [
     "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
     "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
     "pplb200_i8i8_minmax_quantize_fp16_p2p",
-    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters", "pplb200_i8i8_relayout",
+    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters", "pplb200_i8i8_relayout", "pplb200_i8i8_column_parallel_linear_p2p",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -88,6 +88,7 @@ def _load():
     lib.pplb200_p2p_destroy.argtypes = [vp]
     lib.pplb200_p2p_status.argtypes = [vp, i32]
     lib.pplb200_i8i8_row_parallel_linear_p2p.argtypes = [vp, vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32, vp]
+    lib.pplb200_i8i8_column_parallel_linear_p2p.argtypes = [vp, vp, vp, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32, vp]
     lib.pplb200_i8i8_minmax_quantize_fp16_p2p.argtypes = [vp, vp, vp, i64, i64, f32, i32, vp, vp]
     lib.pplb200_i8i8_gemm_i32.argtypes = [vp, vp, i64, vp, i64, i64, i64, i64, i32, i32, vp, vp, i64]
     lib.pplb200_probe_tensor_peak.argtypes = [vp, i32, i32, i32, vp, i64, vp]
@@ -429,6 +430,20 @@ def row_parallel_linear_p2p(p2p, xq, w, scale_m, scale_n, bias, in_features, out
     _check(lib.pplb200_i8i8_row_parallel_linear_p2p(_stream(), p2p.ctx, _ptr(xq), M, xq.stride(0), _ptr(w), _ptr(bias),
                                                     _ptr(scale_m), _ptr(scale_n), down_m, down_n, in_features,
                                                     out_features, phases, _ptr(out)))
+    return out
+
+
+def column_parallel_linear_p2p(p2p, xq, w_shard, scale_m, scale_n_shard, bias_shard, in_features, out_features, out=None,
+                               phases=3, down_m=TOKEN_DOWN_SCALE, down_n=HIDDEN_DOWN_SCALE):
+    """Column-parallel linear whose gathered fp16 output [M, out_features] is assembled by the GEMM epilogues of all
+    ranks over peer-mapped memory."""
+    import torch
+    M = xq.shape[0]
+    if out is None:
+        out = torch.empty((M, out_features), dtype=torch.float16, device=xq.device)
+    _check(lib.pplb200_i8i8_column_parallel_linear_p2p(_stream(), p2p.ctx, _ptr(xq), M, _ptr(w_shard), _ptr(bias_shard),
+                                                       _ptr(scale_m), _ptr(scale_n_shard), down_m, down_n, in_features,
+                                                       out_features, phases, _ptr(out)))
     return out
 
 

@@ -159,3 +159,46 @@ def test_sharded_quantizer_matches_unsharded(cuda, pplb200, world, M, K):
     finally:
         for c in ctxs:
             c.destroy()
+
+
+@pytest.mark.parametrize("world,M,K,N,with_bias", [
+    (2, 512, 1024, 1024, True),     # whole tiles
+    (4, 300, 512, 1056, False),     # ragged rows, 264-column blocks (ragged 64-column slabs)
+    (8, 2048, 1024, 2048, True),    # one 256-column tile per rank
+    (8, 40, 512, 192, True),        # small batch: 24-column blocks
+    (3, 390, 768, 1560, False),     # odd number of ranks
+    (1, 130, 512, 264, True),       # a single rank
+])
+def test_p2p_column_parallel_gather_matches_unsharded(cuda, pplb200, world, M, K, N, with_bias):
+    """Column-parallel linear with gather_output: every rank's GEMM epilogue stores its fp16 block into every
+    rank's [M, N] area (all ranks on one device here: produce for every rank, then finish for every rank), twice
+    in a row on the same contexts with different inputs.  Bar: bit-identical to the unsharded fused linear, on
+    every rank."""
+    torch = cuda
+    rng = np.random.default_rng(world * 1000 + M)
+    ctxs = [pplb200.P2PContext(r, world, M, N) for r in range(world)]
+    try:
+        for c in ctxs:
+            c.connect_local(ctxs)
+        for it in range(2):
+            x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float16)).cuda()
+            w = torch.from_numpy(rng.integers(-127, 128, (N, K), dtype=np.int8)).cuda()
+            sn = torch.from_numpy((rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)).cuda()
+            bias = torch.from_numpy((rng.standard_normal(N) * 0.02).astype(np.float16)).cuda() if with_bias else None
+            xq, sm = pplb200.minmax_quantize_fp16(x)
+            full = pplb200.column_parallel_linear(xq, w, sm, sn, bias, K, N)
+            nw = N // world
+            outs = [torch.zeros((M, N), dtype=torch.float16, device="cuda") for _ in range(world)]
+            for phase in (1, 2):
+                for r in range(world):
+                    pplb200.column_parallel_linear_p2p(ctxs[r], xq, w[r * nw:(r + 1) * nw], sm, sn[r * nw:(r + 1) * nw],
+                                                       None if bias is None else bias[r * nw:(r + 1) * nw], K, N,
+                                                       out=outs[r], phases=phase)
+            torch.cuda.synchronize()
+            for r in range(world):
+                assert ctxs[r].status() == 0
+                assert torch.equal(outs[r].view(torch.int16), full.view(torch.int16)), "rank %d of %d, round %d" % (r, world, it)
+        assert pplb200.gemm_status() == 0
+    finally:
+        for c in ctxs:
+            c.destroy()

@@ -57,6 +57,28 @@ def _worker(rank, world, tmp):
         time.sleep(0.02)
     p2p.connect([open(os.path.join(tmp, "p2p%d" % r), "rb").read() for r in range(world)])
 
+    # a second context for the column-parallel gather (it keeps the gathered matrix where the row-parallel
+    # operator keeps its partial sums, so the two operators get separate contexts)
+    p2p_col = pplb200.P2PContext(rank, world, 2048, 8192)
+    with open(os.path.join(tmp, "p2pc%d.tmp" % rank), "wb") as f:
+        f.write(p2p_col.handle())
+    os.rename(os.path.join(tmp, "p2pc%d.tmp" % rank), os.path.join(tmp, "p2pc%d" % rank))
+    t0 = time.time()
+    while not all(os.path.exists(os.path.join(tmp, "p2pc%d" % r)) for r in range(world)):
+        if time.time() - t0 > 120:
+            raise RuntimeError("rank %d: peer handles missing" % rank)
+        time.sleep(0.02)
+    p2p_col.connect([open(os.path.join(tmp, "p2pc%d" % r), "rb").read() for r in range(world)])
+
+    # the reference's own row_parallel_linear, when its library was built (same NCCL instance: the communicator is shared)
+    ref = None
+    ref_so = os.path.join(ROOT, "oracle", "_ref", "libref_i8i8.so")
+    if os.path.exists(ref_so):
+        import ctypes
+        ref = ctypes.CDLL(ref_so)
+        vp, i64, i32, f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_float
+        ref.ref_row_parallel_linear.argtypes = [vp, vp, vp, vp, vp, vp, f32, f32, i64, i64, i64, i32, i32, vp, vp, vp, i64, vp]
+
     rng = np.random.default_rng(123)  # same inputs on every rank
     results = {}
     # the last shape is large enough for the peer-memory path's two-chunk schedule (second stream)
@@ -90,7 +112,33 @@ def _worker(rank, world, tmp):
                     y_p2p = pplb200.row_parallel_linear_p2p(p2p, xq[:, k0:k1], w_shard, sm, sn, bias, K, N, phases=7 + 8)
                     ok_p2p = ok_p2p and bool(torch.equal(y_p2p.view(torch.int16), full.view(torch.int16)))
             results["%dx%dx%d row p2p exact" % (M, K, N)] = ok_p2p
+        # An unchanged caller of the reference: every rank quantizes ITS OWN K shard, so the row scales differ from
+        # rank to rank, bias is passed on every rank (applied on rank 0 only), reduction order of the reference.
+        xq_s, sm_s = pplb200.minmax_quantize_fp16(x[:, k0:k1].contiguous())
+        w_s = w[:, k0:k1].contiguous()
+        y_own = pplb200.row_parallel_linear(xq_s, w_s, sm_s, sn, bias, K, N, rank=rank, size=world, comm=comm, reduce_mode=1)
+        if ref is not None:
+            acc_ref = torch.empty((M, N), dtype=torch.int32, device="cuda")
+            y_ref = torch.empty((M, N), dtype=torch.float16, device="cuda")
+            ws_ref = torch.empty((32 << 20,), dtype=torch.uint8, device="cuda")
+            P = lambda t: ctypes.c_void_p(t.data_ptr())
+            rc = ref.ref_row_parallel_linear(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), P(xq_s), P(w_s), P(bias),
+                                             P(sm_s), P(sn), 1.0 / 4096, 1.0 / 8192, M, N, K, rank, world, comm, P(acc_ref),
+                                             P(ws_ref), ws_ref.numel(), P(y_ref))
+            torch.cuda.synchronize()
+            # M = 33 / 300 trip the reference's own cuBLASLt tuning quirk (non power-of-four M): compare where it ran
+            if rc == 0:
+                tol = 4e-3 * y_ref.float().abs().max().item() + 1e-3
+                results["%dx%dx%d per-rank scales: reference order equals the reference" % (M, K, N)] = \
+                    bool((y_own.float() - y_ref.float()).abs().max().item() <= tol)
+        results["%dx%dx%d per-rank scales differ between ranks" % (M, K, N)] = not bool(torch.equal(sm_s.view(torch.int16), sm.view(torch.int16)))
         n0, n1 = wl.shard_rows(N, world, rank)
+        ok_colp = True
+        for _ in range(2):  # peer-memory gather, twice on the same context
+            y_colp = pplb200.column_parallel_linear_p2p(p2p_col, xq, w[n0:n1].contiguous(), sm, sn[n0:n1].contiguous(),
+                                                        bias[n0:n1].contiguous(), K, N)
+            ok_colp = ok_colp and bool(torch.equal(y_colp.view(torch.int16), full.view(torch.int16)))
+        results["%dx%dx%d col gather over peer memory exact" % (M, K, N)] = ok_colp
         gather = torch.empty((world, M, n1 - n0), dtype=torch.float16, device="cuda")
         y_col = pplb200.column_parallel_linear(xq, w[n0:n1].contiguous(), sm, sn[n0:n1].contiguous(),
                                                bias[n0:n1].contiguous(), K, N, rank=rank, size=world, comm=comm,
@@ -102,10 +150,11 @@ def _worker(rank, world, tmp):
         err = (y_ref_order.float() - full.float()).abs().max().item()
         scale = full.float().abs().max().item()
         results[key + " fp16-order close"] = bool(err <= 4e-3 * scale + 1e-3)
-    ok = pplb200.gemm_status() == 0 and p2p.status() == 0
+    ok = pplb200.gemm_status() == 0 and p2p.status() == 0 and p2p_col.status() == 0
     torch.cuda.synchronize()
     file_barrier("p2p_done")  # no rank unmaps its buffer while a peer may still read it
     p2p.destroy()
+    p2p_col.destroy()
     pplb200.nccl_comm_destroy(comm)
     with open(os.path.join(tmp, "rank%d" % rank), "w") as f:
         f.write(repr((ok, results)))
