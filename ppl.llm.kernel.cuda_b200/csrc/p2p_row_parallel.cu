@@ -332,15 +332,14 @@ p2p_quantize_rows_kernel(const half* __restrict__ in, int64_t batch, int64_t dim
             if (threadIdx.x == 0) row_max_s = other;
         }
         __syncthreads();
-        const float amax = row_max_s;
-        const float scale = fmaxf(__fdiv_rn(amax, 127.0f), 1e-7f);
-        const float inv_scale = __frcp_rn(scale);
+        const QuantRow qr = make_quant_row(row_max_s, false);
+        const float scale = qr.scale;
 #pragma unroll
         for (int u = 0; u < UNITS; ++u) {
             const int unit = u * blockDim.x + threadIdx.x;
             if (unit < units)
                 *reinterpret_cast<uint4*>(q + row * dim + ((int64_t)unit << 4)) =
-                    quant16(reinterpret_cast<const __half2*>(&v[u][0]), scale, inv_scale);
+                    quant16<true>(reinterpret_cast<const __half2*>(&v[u][0]), qr);
         }
         if (threadIdx.x == 0) scale_out[row] = __float2half_rn(scale * up_scale);
         __syncthreads(); // row_max_s is reused by the next row

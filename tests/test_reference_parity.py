@@ -49,13 +49,25 @@ def _x(rng, M, K, kind):
         x[:, 0] = 127.0
     elif kind == "tiny":
         x = rng.standard_normal((M, K)) * 1e-6
+    elif kind == "near_ties":
+        # quotients a hair away from half-integers: row maximum 127 (scale 1), values k + 0.5 +- one fp16 ulp
+        k = rng.integers(-100, 100, (M, K)).astype(np.float64)
+        x = k + 0.5 + rng.choice([-1.0, 0.0, 1.0], (M, K)) * np.spacing(np.abs(k + 0.5).astype(np.float16)).astype(np.float64)
+        x[:, 0] = 127.0
+    elif kind == "special":
+        # NaNs are ignored by the row maximum and quantize to 0; a row holding an infinity gets an infinite scale
+        x = rng.standard_normal((M, K))
+        x[rng.integers(0, M, 8), rng.integers(0, K, 8)] = np.nan
+        x[M // 2, 3] = np.inf
+        x[M - 1, K - 1] = -np.inf
+        x[0, 5] = np.nan
     else:
         raise ValueError(kind)
     return x.astype(np.float16)
 
 
 @pytest.mark.parametrize("M,K", [(16, 4096), (128, 4096), (5, 28672), (40, 512)])
-@pytest.mark.parametrize("kind", ["normal", "outlier", "ties", "tiny"])
+@pytest.mark.parametrize("kind", ["normal", "outlier", "ties", "tiny", "near_ties", "special"])
 def test_quantizer_three_way(cuda, oracle, ref, M, K, kind):
     import pplb200
     rng = np.random.default_rng(M + K)
