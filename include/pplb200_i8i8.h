@@ -383,17 +383,19 @@ int32_t pplb200_i8i8_relayout(pplb200_stream_t stream, const void* src, int32_t 
  * bench.py reports against).  `result24` is a 24-byte device record the launch fills:
  *   uint64 cycles, uint64 nanoseconds (of CTA 0, from first issue to completion), uint32 status, uint32 pad;
  * status != 0 means a bounded wait inside the probe gave up.
- * tensor_peak: every SM issues `mmas_per_cta` back-to-back tcgen05.mma kind::i8 (M 128 x N 256 x K 32 per CTA,
- *   or M 256 x N 256 x K 32 per CTA pair when cta_pairs != 0) on operands resident in shared memory.  With
+ * tensor_peak: every SM issues `mmas_per_cta` back-to-back tcgen05.mma kind::i8 (M 128 x N x K 32 per CTA, or
+ *   M 256 x N x K 32 per CTA pair) on operands resident in shared memory.  shape: bit 0 = CTA pairs, bit 1 = rotate
+ *   over four accumulator tiles (N <= 64), bits 8 and up = N (0 means 256).  With
  *   stream_src != NULL every CTA also keeps bulk copies from that buffer (stream_bytes, >= 32 KiB) into spare
  *   shared memory in flight, one 32 KiB copy per four MMAs -- the fill rate of a GEMM main loop -- so the figure
  *   becomes the ceiling with the copy engine competing for shared memory.  commit_pattern: bits 0-7 = issue a
  *   tcgen05.commit after every that many MMAs (0: only at the end), bit 8 = plus one to the partner CTA,
  *   bit 9 = one multicast commit to both CTAs instead: what releasing operand slots costs the issue stream.
  * stream_read: one launch reads `bytes` (a multiple of 32 KiB is used) from `src` with bulk asynchronous copies
- *   and discards them.
+ *   and discards them; the record's two uint64 then hold the global-timer nanoseconds of the earliest CTA start
+ *   and of the latest CTA end (the launch as the device saw it, without the host's enqueue latency).
  */
-int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream, int32_t cta_pairs, int32_t mmas_per_cta, int32_t commit_pattern,
+int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream, int32_t shape, int32_t mmas_per_cta, int32_t commit_pattern,
                                   const void* stream_src,
                                   int64_t stream_bytes, void* result24);
 int32_t pplb200_probe_stream_read(pplb200_stream_t stream, const void* src, int64_t bytes, void* result24);

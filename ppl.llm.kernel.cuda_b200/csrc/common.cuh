@@ -131,5 +131,6 @@ int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int*
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);
 int32_t gemm_status(int32_t reset);
 void set_stall_counters(void* dev_ptr);
+unsigned long long* stall_counters();
 
 } // namespace pplb200

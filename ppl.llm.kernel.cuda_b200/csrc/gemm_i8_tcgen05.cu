@@ -863,6 +863,7 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
 }
 
 void set_stall_counters(void* dev_ptr) { g_stall_counters = static_cast<unsigned long long*>(dev_ptr); }
+unsigned long long* stall_counters() { return g_stall_counters; }
 
 int32_t gemm_status(int32_t reset) {
     const DeviceInfo* dev = device_info();

@@ -52,7 +52,7 @@ __device__ __forceinline__ void probe_bulk_load(uint32_t dst, const void* src, u
 
 template <bool PAIR>
 __global__ void __launch_bounds__(128, 1)
-tensor_peak_kernel(int mmas, int commit_pattern, ProbeResult* result, const uint8_t* stream_src, long long stream_chunks) {
+tensor_peak_kernel(int mmas, int commit_pattern, int n_cols, int rotate_acc, ProbeResult* result, const uint8_t* stream_src, long long stream_chunks) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t done_bar;
     __shared__ __align__(8) uint64_t load_bar[LOAD_STAGES];
@@ -88,7 +88,7 @@ tensor_peak_kernel(int mmas, int commit_pattern, ProbeResult* result, const uint
     const uint32_t tmem_base = tmem_base_slot;
 
     if (threadIdx.x == 0 && crank == 0) {
-        const uint32_t idesc = ptx::make_i8_idesc(PAIR ? 256 : 128, 256);
+        const uint32_t idesc = ptx::make_i8_idesc(PAIR ? 256 : 128, n_cols);
         const uint64_t adesc = ptx::make_kmajor_sw128_desc(ring);
         const uint64_t bdesc = ptx::make_kmajor_sw128_desc(ring + A_BYTES);
         const unsigned long long c0 = clock64(), n0 = globaltimer_ns();
@@ -99,8 +99,10 @@ tensor_peak_kernel(int mmas, int commit_pattern, ProbeResult* result, const uint
         const uint32_t slot = ptx::smem_addr(&slot_bar);
         for (int i = 0; i < mmas; ++i) {
             const uint32_t k = (uint32_t)i & 3u;
-            if (PAIR) ptx::mma_i8_pair(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, i != 0 ? 1u : 0u);
-            else ptx::mma_i8(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, i != 0 ? 1u : 0u);
+            // rotate_acc: K sub-block k accumulates into its own tile (columns k * 64 ...), four independent chains
+            const uint32_t d = tmem_base + (rotate_acc ? k * 64u : 0u);
+            if (PAIR) ptx::mma_i8_pair(d, adesc + 2u * k, bdesc + 2u * k, idesc, i > 3 ? 1u : 0u);
+            else ptx::mma_i8(d, adesc + 2u * k, bdesc + 2u * k, idesc, i > 3 ? 1u : 0u);
             if (every != 0 && (i + 1) % every == 0) {
                 if (!PAIR) ptx::mma_commit(slot);
                 else if (commit_pattern & 512) ptx::mma_commit_pair_mcast(slot, 3);
@@ -174,6 +176,7 @@ stream_read_kernel(const uint8_t* __restrict__ src, long long chunks, ProbeResul
     __shared__ __align__(8) uint64_t full_bar[SR_STAGES];
     const uint32_t ring = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     if (threadIdx.x != 0) return;
+    atomicMin(&result->cycles, globaltimer_ns()); // stream_read: `cycles` = earliest CTA start, `nanos` = latest CTA end (ns)
     for (int s = 0; s < SR_STAGES; ++s) ptx::mbar_init(ptx::smem_addr(&full_bar[s]), 1);
     ptx::fence_mbar_init();
     // chunk c of this CTA = blockIdx.x + c * gridDim.x; SR_STAGES copies in flight, slot reused once its copy landed
@@ -194,6 +197,7 @@ stream_read_kernel(const uint8_t* __restrict__ src, long long chunks, ProbeResul
             ++issued;
         }
     }
+    atomicMax(&result->nanos, globaltimer_ns());
 }
 
 } // namespace
@@ -203,10 +207,15 @@ using namespace pplb200;
 
 extern "C" {
 
-int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream_, int32_t cta_pairs, int32_t mmas_per_cta, int32_t commit_pattern, const void* stream_src,
+int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream_, int32_t shape, int32_t mmas_per_cta, int32_t commit_pattern, const void* stream_src,
                                   int64_t stream_bytes, void* result24) {
     cudaStream_t stream = (cudaStream_t)stream_;
+    // shape: bit 0 = CTA pairs; bit 1 = four accumulators in rotation (N <= 64); bits 8.. = MMA N (0: 256)
+    const int32_t cta_pairs = shape & 1, rotate_acc = (shape >> 1) & 1;
+    const int32_t n_cols = (shape >> 8) ? (shape >> 8) : 256;
     if (!result24 || mmas_per_cta < 1 || mmas_per_cta > (1 << 22)) return fail(RC_INVALID_VALUE, "bad probe arguments");
+    if (n_cols < 16 || n_cols > 256 || n_cols % (cta_pairs ? 32 : 16) || (rotate_acc && n_cols > 64))
+        return fail(RC_INVALID_VALUE, "bad MMA N for the probe");
     if (stream_src && (!aligned16(stream_src) || stream_bytes < LOAD_BYTES)) return fail(RC_INVALID_VALUE, "bad stream source");
     const uint8_t* src = (const uint8_t*)stream_src;
     const long long chunks = stream_src ? stream_bytes / LOAD_BYTES : 0;
@@ -229,12 +238,12 @@ int32_t pplb200_probe_tensor_peak(pplb200_stream_t stream_, int32_t cta_pairs, i
             return fail(RC_DEVICE_RUNTIME_ERROR, "shared-memory opt-in failed");
         cfg.gridDim = dim3((unsigned)(sms / 2 * 2), 1, 1);
         cfg.attrs = &attr; cfg.numAttrs = 1;
-        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<true>, (int)mmas_per_cta, (int)commit_pattern, res, src, chunks);
+        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<true>, (int)mmas_per_cta, (int)commit_pattern, (int)n_cols, (int)rotate_acc, res, src, chunks);
     } else {
         if (cudaFuncSetAttribute(tensor_peak_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return fail(RC_DEVICE_RUNTIME_ERROR, "shared-memory opt-in failed");
         cfg.gridDim = dim3((unsigned)sms, 1, 1);
-        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<false>, (int)mmas_per_cta, (int)commit_pattern, res, src, chunks);
+        e = cudaLaunchKernelEx(&cfg, tensor_peak_kernel<false>, (int)mmas_per_cta, (int)commit_pattern, (int)n_cols, (int)rotate_acc, res, src, chunks);
     }
     if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "probe launch failed: %s", cudaGetErrorString(e));
     return RC_SUCCESS;
@@ -247,7 +256,9 @@ int32_t pplb200_probe_stream_read(pplb200_stream_t stream_, const void* src, int
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
         return fail(RC_DEVICE_RUNTIME_ERROR, "device query failed");
     ProbeResult* res = (ProbeResult*)result24;
-    if (cudaMemsetAsync(res, 0, sizeof(ProbeResult), stream) != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
+    if (cudaMemsetAsync(res, 0, sizeof(ProbeResult), stream) != cudaSuccess ||
+        cudaMemsetAsync(&res->cycles, 0xff, sizeof(res->cycles), stream) != cudaSuccess)
+        return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
     const int smem = SR_STAGES * SR_CHUNK + 1024;
     if (cudaFuncSetAttribute(stream_read_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return fail(RC_DEVICE_RUNTIME_ERROR, "shared-memory opt-in failed");

@@ -553,9 +553,34 @@ def gemm_stall_profile(fn):
             "epilogue_waits_for_accumulator": float((epi[:, 5] / epi[:, 6]).mean())}
 
 
+def decode_phase_profile(fn):
+    """Runs fn() (which launches the small-batch GEMM once) with the kernel's phase stamps switched on.  Returns, in
+    microseconds of the device's global timer: the span of the launch (earliest CTA start to latest CTA end) and
+    the mean over the CTAs of set-up, main loop, K-split exchange and epilogue."""
+    import torch
+    buf = torch.zeros((296 * 8,), dtype=torch.int64, device="cuda")
+    lib.pplb200_debug_gemm_stall_counters(_ptr(buf))
+    try:
+        fn()
+        torch.cuda.synchronize()
+    finally:
+        lib.pplb200_debug_gemm_stall_counters(None)
+    c = buf.view(296, 8).cpu().numpy().astype("float64")
+    c = c[c[:, 0] > 0]
+    if len(c) == 0:
+        return None
+    us = lambda a: round(float(a) * 1e-3, 2)
+    return {"ctas": int(len(c)), "span_us": us(c[:, 4].max() - c[:, 0].min()),
+            "start_skew_us": us(c[:, 0].max() - c[:, 0].min()),
+            "setup_us": us((c[:, 1] - c[:, 0]).mean()), "main_loop_us": us((c[:, 2] - c[:, 1]).mean()),
+            "main_loop_max_us": us((c[:, 2] - c[:, 1]).max()),
+            "exchange_us": us((c[:, 3] - c[:, 2]).mean()), "epilogue_us": us((c[:, 4] - c[:, 3]).mean())}
+
+
 def stream_read_probe(sizes=(16 << 20, 48 << 20, 384 << 20), pool_bytes=1536 << 20, reps=12):
     """Single-launch read-only bulk-copy stream of `size` bytes, each launch on a different slice of a pool larger
-    than L2 (so the bytes come from HBM).  Returns per size the median launch time and GB/s."""
+    than L2 (so the bytes come from HBM).  Per size: the median device-side duration of the launch (earliest CTA
+    start to latest CTA end, global timer) and the GB/s that gives."""
     import torch
     pool = torch.empty((pool_bytes,), dtype=torch.uint8, device="cuda")
     pool.fill_(1)
@@ -566,17 +591,14 @@ def stream_read_probe(sizes=(16 << 20, 48 << 20, 384 << 20), pool_bytes=1536 << 
         times = []
         for r in range(reps + 2):
             off = (r % slots) * size
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
             _check(lib.pplb200_probe_stream_read(_stream(), ctypes.c_void_p(pool.data_ptr() + off), size, _ptr(rec)))
-            e1.record()
             torch.cuda.synchronize()
-            if _probe_record(rec)[2]:
+            start, end, status, _ = _probe_record(rec)
+            if status:
                 raise RuntimeError("stream read probe: a bounded wait gave up")
             if r >= 2:
-                times.append(e0.elapsed_time(e1))
+                times.append((end - start) * 1e-3)
         times.sort()
         med = times[len(times) // 2]
-        out["%d MiB" % (size >> 20)] = {"us": round(med * 1e3, 2), "gb_per_s": round(size / (med * 1e-3) / 1e9, 1),
-                                        "note": "includes the 24-byte memset node in front of the launch"}
+        out["%d MiB" % (size >> 20)] = {"us": round(med, 2), "gb_per_s": round(size / (med * 1e-6) / 1e9, 1)}
     return out
