@@ -799,9 +799,52 @@ def aux_kernels(steps, warmup):
         ms = _time_steps(_Eager(fn), steps, warmup, 1)
         t = ms / steps * 1e-3
         out[name] = {"shape": [M, K, 2 * D], "us": t * 1e6, "tops": 2.0 * M * 2 * D * K / t / 1e12}
-    if hasattr(pplb200, "stream_read_probe"):
-        # single-launch read-only TMA stream of a weight matrix: what a launch of that size can reach
-        out["tma_stream_read"] = pplb200.stream_read_probe()
+    # single-launch read-only bulk-copy stream: what one launch of a weight matrix's size can reach
+    out["tma_stream_read"] = pplb200.stream_read_probe()
+    del xq, ws_, acc, outs, scratch
+    torch.cuda.empty_cache()
+
+    # where a small-batch GEMM launch spends its time (the kernel's own global-timer stamps), HBM-cold
+    phases = {}
+    for name, (M, K, N) in (("c0", (16, 4096, 4096)), ("c1", (128, 4096, 12288)), ("M16 N12288", (16, 4096, 12288)),
+                            ("M64 N12288", (64, 4096, 12288))):
+        nset = 10
+        a = torch.randint(-127, 128, (M, K), generator=g, device="cuda", dtype=torch.int8)
+        bs = [torch.randint(-127, 128, (N, K), generator=g, device="cuda", dtype=torch.int8) for _ in range(nset)]
+        sm_ = (torch.rand(M, device="cuda") + 0.5).half()
+        sn_ = (torch.rand(N, device="cuda") * 1e-2 + 1e-3).half()
+        bias = torch.randn(N, device="cuda").half()
+        y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        fn = lambda i: pplb200.gemm_i8i8(a, bs[i % nset], mode=pplb200.EPI_DEQUANT_F16, scale_m=sm_, scale_n=sn_, bias=bias, out=y)
+        for i in range(nset):
+            fn(i)
+        torch.cuda.synchronize()
+        cap = _Captured(fn, nset)
+        per_launch = _time_steps(cap, 4 * nset, nset, 1) / (4 * nset) * 1e3
+        prof = pplb200.decode_phase_profile(lambda: fn(3))
+        for _ in range(3):
+            fn(0)
+        warm = pplb200.decode_phase_profile(lambda: fn(0))
+        phases[name] = dict(prof, us_per_launch_in_graph=round(per_launch, 2), l2_warm_main_loop_us=warm["main_loop_us"])
+        del bs, cap
+        torch.cuda.empty_cache()
+    out["small_batch_gemm_phases"] = phases
+
+    # wait counters of the CTA-pair GEMM's MMA / TMA / epilogue threads on c2's shape
+    M, K, N = 4096, 4096, 22016
+    a = torch.randint(-127, 128, (M, K), generator=g, device="cuda", dtype=torch.int8)
+    b = torch.randint(-127, 128, (N, K), generator=g, device="cuda", dtype=torch.int8)
+    sm_ = (torch.rand(M, device="cuda") + 0.5).half()
+    sn_ = (torch.rand(N, device="cuda") * 1e-2 + 1e-3).half()
+    y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    fn = lambda: pplb200.gemm_i8i8(a, b, mode=pplb200.EPI_DEQUANT_F16, scale_m=sm_, scale_n=sn_, out=y)
+    for _ in range(3):
+        fn()
+    st = pplb200.gemm_stall_profile(fn)
+    if st:
+        tiles = -(-M // 256) * -(-N // 256)
+        st["mma_thread_cycles_per_k_block"] = round(st["mma_thread_cycles"] / (tiles / 74.0 * (K // 128)), 1)
+    out["pair_gemm_thread_waits_c2"] = st
     return out
 
 
@@ -836,6 +879,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-t1", action="store_true", help="N > 1: skip the unsharded runs that give the same-run 1-GPU times")
     ap.add_argument("--no-graphs", action="store_true", help="launch eagerly instead of replaying CUDA graphs")
+    ap.add_argument("--no-probe", action="store_true", help="skip the tensor-peak probe (profiling runs); the fraction then uses 2 x bf16")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -850,7 +894,7 @@ def main():
 
     rank, world = _dist_setup(args.gpus)
     peaks = _peaks()
-    tensor_peak = tensor_peak_probe() if impl == "ours" else None
+    tensor_peak = tensor_peak_probe() if (impl == "ours" and not args.no_probe) else None
     import w8a8_workloads as wl
     head = args.workload
     if args.only:
