@@ -203,6 +203,25 @@ int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const v
                                  void* ws, int64_t ws_bytes, void* y, void* y_q, void* y_q_scale);
 
 /*
+ * The same fused linear for callers whose activations and results live in HOST memory (pinned for the copies to be
+ * asynchronous): x_host fp16 [M, K] in, y_host fp16 [M, N] out (and y_q_host int8 [M, N], y_q_scale_host fp16 [M]
+ * with the re-quantize epilogue).  The batch is cut into chunks of `chunk_rows` tokens (0: 1024) and the three steps
+ * of consecutive chunks -- host -> device copy, quantize + GEMM + epilogue on `stream`, device -> host copy -- run on
+ * three streams at once (the two copy streams and their events are created per device at the first call, which
+ * therefore should come before any stream capture), so a large batch costs little more than its slower copy
+ * direction.  Chunking is exact: the per-token quantizer and the epilogue work row by row.  `ws` is DEVICE memory of
+ * pplb200_i8i8_linear_host_workspace_bytes (two sets of staging buffers); weights, scales and bias are device
+ * pointers as in pplb200_i8i8_linear_fp16.  Work enqueued on `stream` after the call runs after the last copy out.
+ * No counterpart in the reference, whose operators take device pointers only.
+ */
+int64_t pplb200_i8i8_linear_host_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode, int64_t chunk_rows);
+int32_t pplb200_i8i8_linear_fp16_host(pplb200_stream_t stream, const void* x_host, const void* W, const void* scale_N,
+                                      const void* optional_bias, int64_t M, int64_t N, int64_t K, float up_scale,
+                                      float down_scale_M, float down_scale_N, int32_t epilogue_mode, float requant_up_scale,
+                                      int64_t chunk_rows, void* ws, int64_t ws_bytes, void* y_host, void* y_q_host,
+                                      void* y_q_scale_host);
+
+/*
  * Tensor-parallel linears.  `nccl_comm` is an ncclComm_t (may be NULL when size == 1).
  *
  * Column parallel: replaces ppl::kernel::llm::cuda::pmx::i8i8::column_parallel_linear

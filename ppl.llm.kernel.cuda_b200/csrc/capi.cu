@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include "../../include/pplb200_i8i8.h"
 
+#include <mutex>
 #include <stdarg.h>
 #include <string.h>
 
@@ -330,6 +331,113 @@ int32_t pplb200_i8i8_relayout(pplb200_stream_t stream, const void* src, int32_t 
     if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & (elem_bytes == 1 ? 3 : 15))
         return fail(RC_INVALID_VALUE, "src / dst must be aligned to four elements");
     return launch_relayout((cudaStream_t)stream, src, src_layout, dst, dst_layout, rows, cols, elem_bytes);
+}
+
+// ---- host-buffer form of the fused linear ----------------------------------------------------
+namespace {
+struct HostPipe { // per device: two copy streams and the events that order them against the caller's stream
+    bool ready = false;
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t start = nullptr, in_done[2] = {}, comp_done[2] = {}, out_done[2] = {};
+};
+HostPipe g_host_pipe[64];
+std::mutex g_host_pipe_mutex; // one enqueue sequence at a time: the events of a device are shared by its callers
+
+HostPipe* host_pipe() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    HostPipe& h = g_host_pipe[dev];
+    if (!h.ready) {
+        if (cudaStreamCreateWithFlags(&h.in, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaStreamCreateWithFlags(&h.out, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&h.start, cudaEventDisableTiming) != cudaSuccess)
+            return nullptr;
+        for (int i = 0; i < 2; ++i)
+            if (cudaEventCreateWithFlags(&h.in_done[i], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&h.comp_done[i], cudaEventDisableTiming) != cudaSuccess ||
+                cudaEventCreateWithFlags(&h.out_done[i], cudaEventDisableTiming) != cudaSuccess)
+                return nullptr;
+        h.ready = true;
+    }
+    return &h;
+}
+
+int64_t host_chunk_rows(int64_t M, int64_t chunk_rows) {
+    if (chunk_rows <= 0) chunk_rows = 1024;
+    return chunk_rows < M ? chunk_rows : M;
+}
+} // namespace
+
+int64_t pplb200_i8i8_linear_host_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode, int64_t chunk_rows) {
+    const int64_t c = host_chunk_rows(M, chunk_rows);
+    const int64_t per_buf = round_up(c * K * 2, WS_ALIGN) + round_up(c * N * 2, WS_ALIGN) +
+                            (epilogue_mode == EPI_DEQUANT_F16_REQUANT_I8 ? round_up(c * N, WS_ALIGN) + round_up(c * 2, WS_ALIGN) : 0) +
+                            round_up(pplb200_i8i8_linear_workspace_bytes(c, N, K, epilogue_mode), WS_ALIGN);
+    return 2 * per_buf;
+}
+
+int32_t pplb200_i8i8_linear_fp16_host(pplb200_stream_t stream_, const void* x_host, const void* W, const void* scale_N,
+                                      const void* optional_bias, int64_t M, int64_t N, int64_t K, float up_scale,
+                                      float down_scale_M, float down_scale_N, int32_t epilogue_mode, float requant_up_scale,
+                                      int64_t chunk_rows, void* ws, int64_t ws_bytes, void* y_host, void* y_q_host,
+                                      void* y_q_scale_host) {
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (epilogue_mode != EPI_DEQUANT_F16 && epilogue_mode != EPI_DEQUANT_F16_REQUANT_I8)
+        return fail(RC_UNSUPPORTED, "linear_fp16_host epilogue must be DEQUANT_F16 or DEQUANT_F16_REQUANT_I8");
+    if (M < 0 || N < 0 || K <= 0) return fail(RC_INVALID_VALUE, "bad extents");
+    if (M == 0 || N == 0) return RC_SUCCESS;
+    const bool requant = epilogue_mode == EPI_DEQUANT_F16_REQUANT_I8;
+    if (!x_host || !y_host || (requant && (!y_q_host || !y_q_scale_host))) return fail(RC_INVALID_VALUE, "null host buffer");
+    const int64_t need = pplb200_i8i8_linear_host_workspace_bytes(M, N, K, epilogue_mode, chunk_rows);
+    if (!ws || ws_bytes < need) return fail(RC_INVALID_VALUE, "workspace too small: %lld < %lld", (long long)ws_bytes, (long long)need);
+    if ((reinterpret_cast<uintptr_t>(ws) & (WS_ALIGN - 1)) != 0) return fail(RC_INVALID_VALUE, "workspace must be 256-byte aligned");
+    std::lock_guard<std::mutex> lock(g_host_pipe_mutex);
+    HostPipe* h = host_pipe();
+    if (!h) return fail(RC_DEVICE_RUNTIME_ERROR, "stream / event set-up failed: %s", cudaGetErrorString(cudaGetLastError()));
+    const int64_t c = host_chunk_rows(M, chunk_rows);
+    const int64_t lin_ws = round_up(pplb200_i8i8_linear_workspace_bytes(c, N, K, epilogue_mode), WS_ALIGN);
+    char* base = (char*)ws;
+    char *xd[2], *yd[2], *yqd[2] = {nullptr, nullptr}, *ysd[2] = {nullptr, nullptr}, *lw[2];
+    for (int b = 0; b < 2; ++b) {
+        xd[b] = base; base += round_up(c * K * 2, WS_ALIGN);
+        yd[b] = base; base += round_up(c * N * 2, WS_ALIGN);
+        if (requant) { yqd[b] = base; base += round_up(c * N, WS_ALIGN); ysd[b] = base; base += round_up(c * 2, WS_ALIGN); }
+        lw[b] = base; base += lin_ws;
+    }
+#define PPLB200_CU(call) do { if ((call) != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "%s failed: %s", #call, cudaGetErrorString(cudaGetLastError())); } while (0)
+    // both copy streams start after whatever the caller has already enqueued on its stream
+    PPLB200_CU(cudaEventRecord(h->start, stream));
+    PPLB200_CU(cudaStreamWaitEvent(h->in, h->start, 0));
+    PPLB200_CU(cudaStreamWaitEvent(h->out, h->start, 0));
+    int64_t chunk = 0;
+    for (int64_t m0 = 0; m0 < M; m0 += c, ++chunk) {
+        const int b = (int)(chunk & 1);
+        const int64_t rows = M - m0 < c ? M - m0 : c;
+        // copy-in: the staging buffer is free once the linear of two chunks ago has read it
+        if (chunk >= 2) PPLB200_CU(cudaStreamWaitEvent(h->in, h->comp_done[b], 0));
+        PPLB200_CU(cudaMemcpyAsync(xd[b], (const char*)x_host + m0 * K * 2, (size_t)(rows * K * 2), cudaMemcpyHostToDevice, h->in));
+        PPLB200_CU(cudaEventRecord(h->in_done[b], h->in));
+        // compute on the caller's stream: needs the chunk's input, and its output buffers copied out (two chunks ago)
+        PPLB200_CU(cudaStreamWaitEvent(stream, h->in_done[b], 0));
+        if (chunk >= 2) PPLB200_CU(cudaStreamWaitEvent(stream, h->out_done[b], 0));
+        const int32_t rc = pplb200_i8i8_linear_fp16(stream_, xd[b], W, scale_N, optional_bias, rows, N, K, up_scale, down_scale_M,
+                                                    down_scale_N, epilogue_mode, requant_up_scale, lw[b], lin_ws, yd[b], yqd[b], ysd[b]);
+        if (rc != RC_SUCCESS) return rc;
+        PPLB200_CU(cudaEventRecord(h->comp_done[b], stream));
+        // copy-out
+        PPLB200_CU(cudaStreamWaitEvent(h->out, h->comp_done[b], 0));
+        PPLB200_CU(cudaMemcpyAsync((char*)y_host + m0 * N * 2, yd[b], (size_t)(rows * N * 2), cudaMemcpyDeviceToHost, h->out));
+        if (requant) {
+            PPLB200_CU(cudaMemcpyAsync((char*)y_q_host + m0 * N, yqd[b], (size_t)(rows * N), cudaMemcpyDeviceToHost, h->out));
+            PPLB200_CU(cudaMemcpyAsync((char*)y_q_scale_host + m0 * 2, ysd[b], (size_t)(rows * 2), cudaMemcpyDeviceToHost, h->out));
+        }
+        PPLB200_CU(cudaEventRecord(h->out_done[b], h->out));
+    }
+    // join: work enqueued on the caller's stream after this call sees the complete host result
+    PPLB200_CU(cudaStreamWaitEvent(stream, h->out_done[0], 0));
+    if (chunk >= 2) PPLB200_CU(cudaStreamWaitEvent(stream, h->out_done[1], 0));
+#undef PPLB200_CU
+    return RC_SUCCESS;
 }
 
 int32_t pplb200_i8i8_gemm_status(int32_t reset) { return gemm_status(reset); }

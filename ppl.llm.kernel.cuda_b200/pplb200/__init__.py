@@ -41,7 +41,7 @@ EXPORTS = [
     "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
     "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
     "pplb200_i8i8_minmax_quantize_fp16_p2p",
-    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters", "pplb200_i8i8_relayout", "pplb200_i8i8_column_parallel_linear_p2p",
+    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters", "pplb200_i8i8_relayout", "pplb200_i8i8_column_parallel_linear_p2p", "pplb200_i8i8_linear_host_workspace_bytes", "pplb200_i8i8_linear_fp16_host",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -75,6 +75,9 @@ def _load():
     lib.pplb200_i8i8_linear_workspace_bytes.restype = i64
     lib.pplb200_i8i8_linear_fp16.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, f32, f32, f32, i32, f32,
                                              vp, i64, vp, vp, vp]
+    lib.pplb200_i8i8_linear_host_workspace_bytes.argtypes = [i64, i64, i64, i32, i64]
+    lib.pplb200_i8i8_linear_host_workspace_bytes.restype = i64
+    lib.pplb200_i8i8_linear_fp16_host.argtypes = [vp, vp, vp, vp, vp, i64, i64, i64, f32, f32, f32, i32, f32, i64, vp, i64, vp, vp, vp]
     lib.pplb200_i8i8_column_parallel_linear.argtypes = [vp, vp, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
                                                         i32, i32, vp, i32, vp, vp, vp, i64, vp]
     lib.pplb200_i8i8_row_parallel_linear.argtypes = [vp, vp, i64, i64, vp, vp, vp, vp, f32, f32, i64, i64, i32,
@@ -327,6 +330,29 @@ class W8A8Linear:
         if self.yq is None:
             return self.y[:M]
         return self.y[:M], self.yq[:M], self.ys[:M]
+
+
+class W8A8LinearHost:
+    """The fused linear on HOST buffers (pinned tensors): activations are copied in, quantized, multiplied and the
+    result copied out chunk by chunk on three streams (pplb200_i8i8_linear_fp16_host).  Owns the device staging."""
+
+    def __init__(self, w, scale_n, bias=None, max_tokens=None, requant=False, chunk_rows=0):
+        import torch
+        self.w, self.scale_n, self.bias = w, scale_n, bias
+        self.N, self.K = w.shape
+        self.max_tokens, self.chunk_rows = max_tokens, chunk_rows
+        self.mode = EPI_DEQUANT_F16_REQUANT_I8 if requant else EPI_DEQUANT_F16
+        need = lib.pplb200_i8i8_linear_host_workspace_bytes(max_tokens, self.N, self.K, self.mode, chunk_rows)
+        self.ws = torch.empty((need,), dtype=torch.uint8, device=w.device)
+
+    def __call__(self, x_host, y_host, yq_host=None, ys_host=None):
+        M = x_host.shape[0]
+        assert M <= self.max_tokens and x_host.shape[1] == self.K and not x_host.is_cuda and not y_host.is_cuda
+        _check(lib.pplb200_i8i8_linear_fp16_host(_stream(), _ptr(x_host), _ptr(self.w), _ptr(self.scale_n), _ptr(self.bias),
+                                                 M, self.N, self.K, TOKEN_UP_SCALE, TOKEN_DOWN_SCALE, HIDDEN_DOWN_SCALE,
+                                                 self.mode, TOKEN_UP_SCALE, self.chunk_rows, _ptr(self.ws), self.ws.numel(),
+                                                 _ptr(y_host), _ptr(yq_host), _ptr(ys_host)))
+        return y_host
 
 
 def column_parallel_linear(xq, w, scale_m, scale_n, bias, in_features, out_features, rank=0, size=1, comm=None,

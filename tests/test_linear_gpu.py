@@ -129,3 +129,35 @@ def test_linear_error_codes(cuda):
     with pytest.raises(pplb200.PplError) as e:
         pplb200.row_parallel_linear(x, w, s, s, None, 64, 64, input_is_parallel=False)
     assert e.value.rc == pplb200.RC_UNSUPPORTED
+
+
+@pytest.mark.parametrize("M,K,N,chunk,requant", [(300, 512, 264, 128, False), (2500, 1024, 1032, 1024, False),
+                                                 (96, 512, 272, 0, True), (1100, 256, 512, 256, True)])
+def test_linear_on_host_buffers_matches_device_path(cuda, oracle, M, K, N, chunk, requant):
+    """pplb200_i8i8_linear_fp16_host: pinned host activations in, pinned host results out, chunks of the batch
+    overlapped on three streams.  Bit-identical to the device-buffer linear (chunking is exact: every step works
+    row by row), called twice in a row on the same staging buffers with different inputs."""
+    import pplb200
+    rng = np.random.default_rng(M + K + N)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    sn = (rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float16)
+    tw, tsn, tb = _t(cuda, w), _t(cuda, sn), _t(cuda, bias)
+    host = pplb200.W8A8LinearHost(tw, tsn, tb, max_tokens=M, requant=requant, chunk_rows=chunk)
+    dev = pplb200.W8A8Linear(tw, tsn, tb, max_tokens=M, requant=requant)
+    y_host = cuda.empty((M, N), dtype=cuda.float16).pin_memory()
+    yq_host = cuda.empty((M, N), dtype=cuda.int8).pin_memory() if requant else None
+    ys_host = cuda.empty((M,), dtype=cuda.float16).pin_memory() if requant else None
+    for it in range(2):
+        x = cuda.from_numpy(rng.standard_normal((M, K)).astype(np.float16)).pin_memory()
+        host(x, y_host, yq_host, ys_host)
+        want = dev(x.cuda())
+        cuda.cuda.synchronize()
+        if requant:
+            assert cuda.equal(y_host.view(cuda.int16), want[0].cpu().view(cuda.int16))
+            assert cuda.equal(yq_host, want[1].cpu()) and cuda.equal(ys_host.view(cuda.int16), want[2].cpu().view(cuda.int16))
+        else:
+            assert cuda.equal(y_host.view(cuda.int16), want.cpu().view(cuda.int16)), it
+    ref = oracle.linear(x.numpy()[:8], w, sn, bias)
+    assert np.array_equal(oracle.f16_bits(y_host[:8].numpy()), oracle.f16_bits(ref["y"]))
+    assert pplb200.gemm_status() == 0
