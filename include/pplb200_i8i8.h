@@ -354,7 +354,10 @@ int32_t pplb200_i8i8_column_parallel_linear_p2p(pplb200_stream_t stream, void* c
  * batch <= 16384, shard_dim % 16 == 0, shard_dim <= 32768; all ranks call it with the same batch,
  * in the same order on their contexts.  phases: 3 for the operation; 1 only publishes the shard
  * maxima (lets one process that drives several ranks on one stream run "1" for every rank and then
- * "3" for every rank).  A wait that expires sets bit 2 of pplb200_p2p_status.
+ * "3" for every rank; a "1" must be followed by a "3" on the SAME input before anything else is quantized on the
+ * context: it publishes under the tag of the operation that the "3" completes).  The kernel is launched
+ * cooperatively (the whole grid resident at once, or the launch fails): keep the device free enough for it.
+ * A wait that expires sets bit 2 of pplb200_p2p_status.
  */
 int32_t pplb200_i8i8_minmax_quantize_fp16_p2p(pplb200_stream_t stream, void* ctx, const void* input, int64_t batch,
                                               int64_t shard_dim, float up_scale, int32_t phases,

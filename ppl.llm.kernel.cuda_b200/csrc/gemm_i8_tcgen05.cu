@@ -18,7 +18,6 @@
 
 #include <mutex>
 #include <string.h>
-#include <stdlib.h>
 
 namespace pplb200 {
 
@@ -49,7 +48,6 @@ struct KernelParams {
     unsigned int* status;
     // optional diagnostics: 8 x uint64 per CTA (cycles the MMA / producer / epilogue threads spent in their waits)
     unsigned long long* stall;
-    int32_t exp_flags; // experiment switches (environment PPLB200_EXP), 0 in production
     // EPI_RAW_I32 with raw_affine != 0: out = raw_alpha * acc + raw_beta * out + raw_bias[n] (wrapping int32)
     int32_t raw_affine, raw_alpha, raw_beta;
     const int32_t* raw_bias;
@@ -725,7 +723,6 @@ unsigned long long* g_stall_counters = nullptr;
 
 void fill_common(KernelParams& p, const GemmArgs& a, unsigned int* status) {
     p.stall = g_stall_counters;
-    { const char* e = getenv("PPLB200_EXP"); p.exp_flags = e ? atoi(e) : 0; }
     p.M = (int32_t)a.M; p.N = (int32_t)a.N;
     p.num_k_blocks = (int32_t)((a.K + BK - 1) / BK);
     p.mode = a.mode;

@@ -659,7 +659,13 @@ static int32_t launch_p2p_quantize(cudaStream_t stream, const Ctx& c, const half
         return fail(RC_DEVICE_RUNTIME_ERROR, "occupancy query failed");
     int64_t grid = (int64_t)per_sm * sms; // every CTA resident: none waits for an SM while its row is awaited elsewhere
     if (grid > batch) grid = batch;
-    p2p_quantize_rows_kernel<UNITS><<<(unsigned)grid, threads, 0, stream>>>(in, batch, dim, up_scale, q, scale, peers_of(c), publish_only);
+    // Cooperative launch: the grid starts only when all of it can be resident at once -- which is what lets every CTA
+    // publish all its rows before any CTA waits -- and a grid that could never fit is refused.  An ordinary launch may
+    // start part of the grid behind other work; the ranks would then stall each other until their bounded waits ran out.
+    Peers pr = peers_of(c);
+    void* args[] = {(void*)&in, (void*)&batch, (void*)&dim, (void*)&up_scale, (void*)&q, (void*)&scale, (void*)&pr, (void*)&publish_only};
+    const cudaError_t e = cudaLaunchCooperativeKernel((const void*)p2p_quantize_rows_kernel<UNITS>, dim3((unsigned)grid), dim3(threads), args, 0, stream);
+    if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "sharded quantizer launch failed: %s", cudaGetErrorString(e));
     return check_launch("minmax_quantize_fp16_p2p");
 }
 

@@ -107,12 +107,6 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
     asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// Asks the TMA unit to bring the box at (x, y) into L2 (no shared-memory destination, no completion signal).
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* m, int32_t x, int32_t y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];"
-                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y) : "memory");
-}
-
 // ---- tcgen05 / TMEM ---------------------------------------------------------------------------
 
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) { // whole warp

@@ -96,11 +96,13 @@ def _worker(rank, world, tmp):
         y_ref_order = pplb200.row_parallel_linear(xq[:, k0:k1], w[:, k0:k1].contiguous(), sm, sn, bias, K, N,
                                                   rank=rank, size=world, comm=comm, reduce_mode=1)
         if K % (16 * world) == 0:  # sharded quantizer: every rank passes only its K shard
-            x_shard = x[:, k0:k1].contiguous()
             ok_q = True
-            for _ in range(3):
-                q_p2p, s_p2p = pplb200.minmax_quantize_fp16_p2p(p2p, x_shard)
-                ok_q = ok_q and bool(torch.equal(q_p2p, xq[:, k0:k1])) and bool(torch.equal(s_p2p.view(torch.int16), sm.view(torch.int16)))
+            for rnd in range(3):  # new activations every round, the row maximum moving from shard to shard
+                x_r = x.clone()
+                x_r[:, (rnd * 37) % K::world] *= 3.0 + rnd
+                xq_r, sm_r = pplb200.minmax_quantize_fp16(x_r)
+                q_p2p, s_p2p = pplb200.minmax_quantize_fp16_p2p(p2p, x_r[:, k0:k1].contiguous())
+                ok_q = ok_q and bool(torch.equal(q_p2p, xq_r[:, k0:k1])) and bool(torch.equal(s_p2p.view(torch.int16), sm_r.view(torch.int16)))
             results["%dx%d sharded quantizer exact" % (M, K)] = ok_q
         if M % world == 0:
             w_shard = w[:, k0:k1].contiguous()
