@@ -335,10 +335,11 @@ def build_ours(wk):
         xq, sm = pplb200.minmax_quantize_fp16(wk.x[0])
         mode = pplb200.EPI_DEQUANT_F16
         ys = [l.y for l in lins]
+        gws = torch.empty((max(pplb200.gemm_workspace_bytes(M, Nw, K, mode), 256),), dtype=torch.uint8, device=dev)
 
         def kernel_only(i):
             s = i % wk.nsets
-            pplb200.gemm_i8i8(xq, wk.w[s], mode=mode, scale_m=sm, scale_n=wk.sn, bias=wk.bias, out=ys[s])
+            pplb200.gemm_i8i8(xq, wk.w[s], mode=mode, scale_m=sm, scale_n=wk.sn, bias=wk.bias, ws=gws, out=ys[s])
 
         gemm_bytes = M * K + Nw * K + 2 * Nw + (2 * Nw if wk.bias is not None else 0) + 2 * M + 2 * M * Nw
         launches = 2 + (1 if requant else 0)

@@ -390,6 +390,14 @@ int32_t pplb200_i8i8_gemm_status(int32_t reset);
 void pplb200_debug_gemm_stall_counters(void* counters);
 
 /*
+ * Diagnostics (process-wide switch, not thread-safe, on by default): when few 256 x 256 output tiles are left over
+ * after the full waves of one tile per CTA pair, the CTA-pair GEMM cuts them along K into slices that different pairs
+ * compute at once and sums the slices in the workspace (integer sums: the result does not depend on it).
+ * enabled = 0 computes every tile on one pair, for A/B timing.
+ */
+void pplb200_debug_gemm_tail_split(int32_t enabled);
+
+/*
  * Storage-order change of a [rows, cols] matrix of int8 (elem_bytes 1) or int32 (elem_bytes 4) elements between
  * any two of ROW_MAJOR, COL32, COL32_2R_4R4 and COL4_4R2_8C (index maps of
  * include/ppl/kernel/llm/cuda/common/matrix_layout.h:34-142; no counterpart function in the reference, whose

@@ -33,8 +33,15 @@ namespace {
 
 constexpr int64_t WS_ALIGN = 256;
 
-int64_t gemm_ws_bytes(int64_t M, int32_t mode) {
+// row maxima of the fused re-quantize
+int64_t absmax_ws_bytes(int64_t M, int32_t mode) {
     return mode == EPI_DEQUANT_F16_REQUANT_I8 ? round_up(M * 4, WS_ALIGN) : 0;
+}
+// What the GEMM asks for: the row maxima, then (large batches only) the scratch through which CTA pairs share the
+// tiles of the last waves.  The second part is optional at run time: with a smaller workspace every tile is computed
+// by one pair.
+int64_t gemm_ws_bytes(int64_t M, int32_t mode) {
+    return absmax_ws_bytes(M, mode) + (M > 128 ? kSkWsBytes : 0);
 }
 
 int32_t check_gemm_args(const void* A, int64_t lda, const void* B, int64_t ldb, int64_t M, int64_t N, int64_t K,
@@ -78,12 +85,16 @@ int32_t gemm_entry(cudaStream_t stream, const void* A, int64_t lda, const void* 
     g.down_m = down_M; g.down_n = down_N;
     g.out = out; g.ldc = ldc;
     g.row_absmax_bits = nullptr;
+    const int64_t need = absmax_ws_bytes(M, mode);
     if (mode == EPI_DEQUANT_F16_REQUANT_I8) {
-        const int64_t need = gemm_ws_bytes(M, mode);
         if (!ws || ws_bytes < need) return fail(RC_INVALID_VALUE, "workspace too small: %lld < %lld", (long long)ws_bytes, (long long)need);
         g.row_absmax_bits = (uint32_t*)ws;
         if (!chained && cudaMemsetAsync(ws, 0, (size_t)M * 4, stream) != cudaSuccess)
             return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
+    }
+    if (ws && ws_bytes > need) {
+        g.sk_ws = (char*)ws + need;
+        g.sk_ws_bytes = ws_bytes - need;
     }
     g.pdl = chained;
     rc = launch_gemm(stream, g);
@@ -442,6 +453,7 @@ int32_t pplb200_i8i8_linear_fp16_host(pplb200_stream_t stream_, const void* x_ho
 
 int32_t pplb200_i8i8_gemm_status(int32_t reset) { return gemm_status(reset); }
 void pplb200_debug_gemm_stall_counters(void* counters) { set_stall_counters(counters); }
+void pplb200_debug_gemm_tail_split(int32_t enabled) { set_tail_split(enabled != 0); }
 
 // Host helper for tests: the library's (row, col) -> offset map for a layout.
 int64_t pplb200_layout_offset(int32_t layout, int64_t rows, int64_t cols, int64_t row, int64_t col) {

@@ -126,11 +126,24 @@ struct GemmArgs {
     // rank d < gather_ranks (ldc = width of the gathered output)
     int32_t gather_ranks = 0;
     int64_t gather_col0 = 0;
+    // Optional scratch (256-byte aligned, kSkWsBytes, contents arbitrary) that lets the CTA-pair kernel cut the few
+    // tiles left over after its full waves along K and compute the slices on different pairs at once; without it every
+    // tile is computed by one pair.  Two launches that may run at the same time need separate scratches.
+    void* sk_ws = nullptr;
+    int64_t sk_ws_bytes = 0;
 };
+// at most kSkMaxTiles leftover tiles (half the CTA pairs of a 148-SM device) of 256 x 256 int32 partial sums,
+// preceded by the warps' arrival counters
+constexpr int64_t kSkMaxTiles = 40;
+constexpr int64_t kSkTileBytes = 256 * 256 * 4;
+constexpr int64_t kSkStateBytes = 2048;
+constexpr int64_t kSkWsBytes = kSkStateBytes + kSkMaxTiles * kSkTileBytes;
+static_assert(kSkMaxTiles * 8 * 4 <= kSkStateBytes, "arrival counters");
 int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int* status, bool pdl);
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);
 int32_t gemm_status(int32_t reset);
 void set_stall_counters(void* dev_ptr);
+void set_tail_split(bool on);
 unsigned long long* stall_counters();
 
 } // namespace pplb200

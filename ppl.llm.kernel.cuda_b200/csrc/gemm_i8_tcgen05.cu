@@ -57,6 +57,12 @@ struct KernelParams {
     // EPI_PUSH_I32 (CTA-pair kernel only): see GemmArgs
     int32_t* push_base[kMaxPeers];
     int32_t push_rows, push_rank;
+    // CTA-pair kernel, K slices of the leftover tiles (see WorkIter): tiles [0, full_tiles) are computed whole; each
+    // later tile as k_slices items whose int32 partial tiles are added into sk_scratch[tile - full_tiles][256][256];
+    // sk_arrivals[(tile - full_tiles) * 8 + cta * 4 + warp] counts the slices delivered.
+    int32_t full_tiles, k_slices;
+    unsigned int* sk_arrivals;
+    int32_t* sk_scratch;
     // EPI_GATHER_F16 (CTA-pair kernel only): see GemmArgs
     int32_t gather_ranks;
     int64_t gather_col0;
@@ -116,12 +122,29 @@ __device__ __forceinline__ uint4 ld_shared_v4_epi(uint32_t addr) {
 // at the matrix bounds (no per-element predicates, no partial sectors).
 constexpr int EPI_STAGE_BYTES = 4 * 2 * 4096;
 
+// accumulator columns c .. c + 31 of this lane's row: from tensor memory, or (sums != nullptr) from this lane's row
+// of a K-sliced tile's summed int32 scratch (written by other SMs' reductions: loads that bypass L1)
+__device__ __forceinline__ void load_acc32(uint32_t taddr_row, const int32_t* sums, int c, uint32_t (&acc)[32]) {
+    if (sums == nullptr) {
+        ptx::tmem_ld_32x32(taddr_row + c, acc);
+        ptx::tmem_ld_wait();
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int4 v = __ldcg(reinterpret_cast<const int4*>(sums + c) + j);
+            acc[4 * j] = (uint32_t)v.x; acc[4 * j + 1] = (uint32_t)v.y; acc[4 * j + 2] = (uint32_t)v.z; acc[4 * j + 3] = (uint32_t)v.w;
+        }
+    }
+}
+
 // Drains this warp's 32 lanes x BN accumulator columns (TMEM address taddr_row) for output rows
 // row0 .. row0 + 31 and columns n_base .. n_base + BN - 1: RAW_I32, DEQUANT_F16 or DEQUANT_F16_REQUANT_I8.
 // `stage` = shared-memory address of the warp's two buffers; `sel` counts the slabs stored so far.
+// `sums`: see load_acc32.
 template <int BN>
 __device__ __forceinline__ void drain_tile(const KernelParams& p, const CUtensorMap* tmap_out, uint32_t taddr_row,
-                                           int row0, int n_base, int lane, uint32_t stage, uint32_t& sel) {
+                                           int row0, int n_base, int lane, uint32_t stage, uint32_t& sel,
+                                           const int32_t* sums = nullptr) {
     const int row = row0 + lane;
     const bool row_ok = row < p.M;
     const uint32_t my_row = (uint32_t)lane * 128u, sw = (uint32_t)(lane & 7);
@@ -131,8 +154,7 @@ __device__ __forceinline__ void drain_tile(const KernelParams& p, const CUtensor
             const int n0 = n_base + c0;
             if (n0 >= p.N) break; // warp-uniform
             uint32_t acc[32];
-            ptx::tmem_ld_32x32(taddr_row + c0, acc);
-            ptx::tmem_ld_wait();
+            load_acc32(taddr_row, sums, c0, acc);
             if (p.raw_affine) {
                 const int32_t* old = reinterpret_cast<const int32_t*>(p.out) + (int64_t)row * p.ldc + n0;
 #pragma unroll
@@ -179,8 +201,7 @@ __device__ __forceinline__ void drain_tile(const KernelParams& p, const CUtensor
             const int nn = n0 + 32 * h;
             if (nn >= p.N) break; // warp-uniform; the box is clipped at column N
             uint32_t acc[32];
-            ptx::tmem_ld_32x32(taddr_row + c0 + 32 * h, acc);
-            ptx::tmem_ld_wait();
+            load_acc32(taddr_row, sums, c0 + 32 * h, acc);
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
                 if (nn + j >= p.N) break;
@@ -337,6 +358,38 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 }
 
 
+// The work of one CTA pair, in order.  The persistent grid runs in waves of one tile per pair; a tile count that is not
+// a multiple of the pair count would leave most pairs idle during the last wave.  So when few tiles are left over
+// (at most half as many as there are pairs), each of them is cut along K into k_slices items that different pairs
+// compute at the same time, and these items come FIRST: a slice is the first item of its pair, the whole tiles
+// (tile = pair + wave * pairs) follow.  A slice's int32 partial tile is added into a zeroed scratch tile by the TMA
+// unit's reduction; the warp that delivers the last slice of its 32 rows reads the sums back and runs the real
+// epilogue (integer sums: exact in any order; nobody waits for anybody).  Coming first, all of that -- the
+// reductions, the counting, the read-back -- runs under the main loop of the pair's next tile instead of after the
+// end of the kernel, and slices with the same index stay in step along K, so tiles that share an operand panel
+// still fetch it from L2 together.
+struct WorkIter {
+    int slice, tile_next, stride, full_tiles, nkb, k_slices;
+    __device__ __forceinline__ WorkIter(const KernelParams& p, int num_tiles, int pair_id, int num_pairs) {
+        full_tiles = p.full_tiles; nkb = p.num_k_blocks; k_slices = p.k_slices; stride = num_pairs; tile_next = pair_id;
+        slice = pair_id < (num_tiles - full_tiles) * k_slices ? pair_id : -1;
+    }
+    // next item: K blocks [kb0, kb0 + cnt) of `tile`
+    __device__ __forceinline__ bool next(int& tile, int& kb0, int& cnt) {
+        if (slice >= 0) {
+            const int t = slice / k_slices, s = slice - t * k_slices;
+            tile = full_tiles + t;
+            kb0 = (int)((long long)nkb * s / k_slices);
+            cnt = (int)((long long)nkb * (s + 1) / k_slices) - kb0;
+            slice = -1;
+            return true;
+        }
+        if (tile_next >= full_tiles) return false;
+        tile = tile_next; tile_next += stride; kb0 = 0; cnt = nkb;
+        return true;
+    }
+};
+
 // ---- CTA-pair variant ---------------------------------------------------------------------------
 // Two CTAs of a cluster compute one 256 x 256 tile with tcgen05.mma.cta_group::2: each CTA stages
 // its own 128 rows of A and its own 128 rows of B (half of the tile's N), the leader issues the
@@ -360,7 +413,8 @@ struct PairCfg {
 template <int EW>
 __global__ void __launch_bounds__(64 + 32 * EW, 1)
 gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const __grid_constant__ CUtensorMap tmap_out, const KernelParams p) {
+                            const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_sk,
+                            const KernelParams p) {
     using C = PairCfg;
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[C::STAGES];   // used in the leader: both CTAs' tiles have landed
@@ -414,7 +468,9 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             long long t_wait = 0;
             const long long t_begin = clock64();
             const uint32_t full_local0 = ptx::smem_addr(&full_bar[0]), full_leader0 = ptx::map_to_cta(full_local0, 0);
-            for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs) {
+            WorkIter work(p, num_tiles, pair_id, num_pairs);
+            int tile, kb0, cnt;
+            while (ok && work.next(tile, kb0, cnt)) {
                 const int m_tile = tile % p.num_m_tiles;
                 const int n_tile = tile / p.num_m_tiles;
                 const int row_a = m_tile * 256 + (int)rank * BM;
@@ -422,7 +478,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                 // output channels, so accumulator columns [0,128) and [128,256) pair up element by element
                 const int row_b = p.mode == EPI_SWIGLU_F16 ? n_tile * C::HALF_N + (int)rank * p.act_dim
                                                            : n_tile * C::BN + (int)rank * C::HALF_N;
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = kb0; kb < kb0 + cnt; ++kb) {
                     const long long tw = p.stall ? clock64() : 0;
                     if (!ptx::mbar_wait(ptx::smem_addr(&empty_bar[stage]), phase ^ 1u, p.status, ST_PRODUCER_TIMEOUT)) {
                         ok = false;
@@ -452,14 +508,16 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             bool ready = false;
             long long t_full = 0, t_acc = 0;
             const long long t_begin = clock64();
-            for (int tile = pair_id; tile < num_tiles && ok; tile += num_pairs, ++it) {
+            WorkIter work(p, num_tiles, pair_id, num_pairs);
+            int tile, kb0, cnt;
+            for (; ok && work.next(tile, kb0, cnt); ++it) {
                 const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
                 const long long ta = p.stall ? clock64() : 0;
                 if (!ptx::mbar_wait(ptx::smem_addr(&acc_empty_bar[buf]), acc_phase ^ 1u, p.status, ST_MMA_ACC_TIMEOUT)) break;
                 if (p.stall) t_acc += clock64() - ta;
                 ptx::tc_fence_after();
                 const uint32_t tmem_d = tmem_base + buf * C::BN;
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = 0; kb < cnt; ++kb) {
                     if (!ready) { // the poll issued one iteration ago found the stage still empty: wait for it
                         const long long tw = p.stall ? clock64() : 0;
                         if (!ptx::mbar_wait(full0 + stage * 8u, phase, p.status, ST_MMA_FULL_TIMEOUT)) {
@@ -499,7 +557,9 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         int it = 0;
         long long t_accfull = 0;
         const long long t_begin = clock64();
-        for (int tile = pair_id; tile < num_tiles; tile += num_pairs, ++it) {
+        WorkIter work(p, num_tiles, pair_id, num_pairs);
+        int tile, kb0, cnt;
+        for (; work.next(tile, kb0, cnt); ++it) {
             const int m_tile = tile % p.num_m_tiles;
             const int n_tile = tile / p.num_m_tiles;
             const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
@@ -513,6 +573,52 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             float batch_scale = 0.0f;
             if (p.mode == EPI_SWIGLU_F16 && row_ok) batch_scale = __fmul_rn(__half2float(p.scale_m[row]), p.down_m);
             const uint32_t taddr_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::BN;
+            const int32_t* sums = nullptr; // set when the accumulators come from a K-sliced tile's scratch
+
+            if (EW == 4 && cnt < nkb) {
+                // One K slice of a leftover tile: this warp's 32 x 256 partial block is ADDED into the scratch tile, 32 x 32
+                // slab by slab through the staging buffers, by the TMA unit's tiled reduction (whole 128-byte lines).
+                const int t = tile - p.full_tiles;
+                const int srow0 = t * 256 + (int)rank * BM + quarter * 32;
+                const uint32_t stage = ptx::smem_addr(epi_stage) + (uint32_t)(warp - 2) * 8192u;
+                const uint32_t my_row = (uint32_t)lane * 128u, sw = (uint32_t)(lane & 7);
+#pragma unroll 1
+                for (int c0 = 0; c0 < C::BN; c0 += 32) {
+                    uint32_t acc[32];
+                    ptx::tmem_ld_32x32(taddr_row + c0, acc);
+                    ptx::tmem_ld_wait();
+                    const uint32_t sbuf = stage + (sel & 1u) * 4096u;
+                    if (lane == 0) ptx::bulk_wait_group_read<1>(); // the copy that last used this buffer has read it
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        ptx::st_shared_v4(sbuf + my_row + (((uint32_t)j ^ sw) << 4), make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        ptx::tma_reduce_add_2d(&tmap_sk, sbuf, c0, srow0);
+                        ptx::bulk_commit_group();
+                    }
+                    ++sel;
+                }
+                // the accumulator buffer is free again
+                ptx::tc_fence_before();
+                __syncwarp();
+                unsigned int arrived = 0;
+                if (lane == 0) {
+                    ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
+                    // last slice of these 32 rows to arrive?  (additions performed -> fences -> count; count -> fence -> reads)
+                    ptx::bulk_wait_group<0>();     // performed, not merely read from shared memory
+                    ptx::fence_proxy_async_all();  // ... by the async proxy: order them before the count
+                    __threadfence();
+                    arrived = atomicAdd(p.sk_arrivals + t * 8 + (int)rank * 4 + quarter, 1u);
+                }
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                if (arrived != (unsigned int)p.k_slices - 1u) continue;
+                // this warp delivered the last slice: the sums are complete; run the epilogue proper from them
+                __threadfence();
+                sums = p.sk_scratch + (int64_t)(srow0 + lane) * 256;
+            }
 
             if (p.mode == EPI_SWIGLU_F16) {
                 // out[m, n] = fp16( silu_beta(dq(x)) * dq(gate) ), operation order of the reference's
@@ -577,8 +683,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                     const int n0 = n_tile * C::BN + c0;
                     if (n0 >= p.N) break; // warp-uniform
                     uint32_t acc[32];
-                    ptx::tmem_ld_32x32(taddr_row + c0, acc);
-                    ptx::tmem_ld_wait();
+                    load_acc32(taddr_row, sums, c0, acc);
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         tr[lane * 8 + (j ^ (lane & 7))] = make_uint4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
@@ -592,6 +697,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                     }
                     __syncwarp();
                 }
+                if (sums != nullptr) continue; // the accumulator buffer was handed back when the slice was delivered
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
@@ -619,8 +725,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                         const int nn = n0 + 32 * h;
                         if (nn >= p.N) break;
                         uint32_t acc[32];
-                        ptx::tmem_ld_32x32(taddr_row + c0 + 32 * h, acc);
-                        ptx::tmem_ld_wait();
+                        load_acc32(taddr_row, sums, c0 + 32 * h, acc);
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
                             if (nn + j >= p.N) break;
@@ -641,6 +746,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                     }
                     __syncwarp();
                 }
+                if (sums != nullptr) continue; // the accumulator buffer was handed back when the slice was delivered
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&acc_empty_bar[buf]), 0));
@@ -649,7 +755,8 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
 
             if (EW == 4)
                 drain_tile<C::BN>(p, &tmap_out, taddr_row, m_tile * 256 + (int)rank * BM + quarter * 32, n_tile * C::BN, lane,
-                                  ptx::smem_addr(epi_stage) + (uint32_t)(warp - 2) * 8192u, sel);
+                                  ptx::smem_addr(epi_stage) + (uint32_t)(warp - 2) * 8192u, sel, sums);
+            if (sums != nullptr) continue; // the accumulator buffer was handed back when the slice was delivered
 
             // this CTA's half of the accumulator buffer is drained: tell the leader's MMA thread
             ptx::tc_fence_before();
@@ -717,6 +824,9 @@ bool make_output_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t
               elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+// Diagnostics switch (pplb200_debug_gemm_tail_split): false = whole tiles only, whatever the tile count.
+bool g_slice_leftover_tiles = true;
 
 // Diagnostics switch (pplb200_debug_gemm_stall_counters): device array the CTA-pair kernel fills when non-null.
 unsigned long long* g_stall_counters = nullptr;
@@ -791,7 +901,8 @@ int32_t launch_bn(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev)
 
 // 256 x 256 tiles on CTA pairs (clusters of two), persistent: one pair per two SMs.
 int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& dev) {
-    CUtensorMap ta, tb, tc;
+    CUtensorMap ta, tb, tc, tsk;
+    memset(&tsk, 0, sizeof(tsk)); // scratch tiles of the K slices; only touched when leftover tiles are sliced
     if (!make_operand_map(&ta, a.A, a.M, a.K, a.lda, BM)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (A) encode failed");
     if (!make_operand_map(&tb, a.B, a.N, a.K, a.ldb, PairCfg::HALF_N)) return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (B) encode failed");
     memset(&tc, 0, sizeof(tc)); // the SwiGLU and push epilogues store with their own instructions and never touch it
@@ -814,6 +925,28 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
     int64_t pairs = dev.sms / 2;
     if (tiles < pairs) pairs = tiles;
+    // Few tiles left over after the full waves: cut them along K (see WorkIter), if the caller's workspace holds the
+    // scratch tiles.  Not for SwiGLU (eight epilogue warps, paired accumulator halves).
+    p.full_tiles = (int32_t)tiles; p.k_slices = 1;
+    const int64_t rest = tiles % pairs;
+    if (rest != 0 && g_slice_leftover_tiles && a.mode != EPI_SWIGLU_F16 && rest <= kSkMaxTiles && a.sk_ws != nullptr &&
+        a.sk_ws_bytes >= kSkWsBytes && (reinterpret_cast<uintptr_t>(a.sk_ws) & 255) == 0) {
+        int64_t f = pairs / rest;
+        if (f > 8) f = 8;
+        if (f > p.num_k_blocks / 4) f = p.num_k_blocks / 4; // at least four K blocks per slice
+        // Worth it when the K blocks saved -- (1 - 1/f) of a tile -- outweigh what slicing costs: clearing, adding
+        // to and reading back `rest` scratch tiles, measured at about 1.25 K blocks' time per tile plus a fixed 13.
+        if (f >= 2 && 4 * (f - 1) * p.num_k_blocks >= f * (52 + 5 * rest)) {
+            if (cudaMemsetAsync(a.sk_ws, 0, (size_t)(kSkStateBytes + rest * kSkTileBytes), stream) != cudaSuccess)
+                return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
+            p.sk_arrivals = static_cast<unsigned int*>(a.sk_ws);
+            p.sk_scratch = reinterpret_cast<int32_t*>(static_cast<char*>(a.sk_ws) + kSkStateBytes);
+            if (!make_output_map(&tsk, p.sk_scratch, rest * 256, 256, 256, 4))
+                return fail(RC_DEVICE_RUNTIME_ERROR, "tensor map (slice scratch) encode failed");
+            p.full_tiles = (int32_t)(tiles - rest);
+            p.k_slices = (int32_t)f;
+        }
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     const bool wide_epilogue = a.mode == EPI_SWIGLU_F16;
@@ -827,8 +960,8 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = wide_epilogue ? cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<8>, ta, tb, tc, p)
-                                        : cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<4>, ta, tb, tc, p);
+    const cudaError_t e = wide_epilogue ? cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<8>, ta, tb, tc, tsk, p)
+                                        : cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<4>, ta, tb, tc, tsk, p);
     if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "pair GEMM launch failed: %s", cudaGetErrorString(e));
     return RC_SUCCESS;
 }
@@ -859,6 +992,7 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     return launch_bn<64>(stream, a, *dev);
 }
 
+void set_tail_split(bool on) { g_slice_leftover_tiles = on; }
 void set_stall_counters(void* dev_ptr) { g_stall_counters = static_cast<unsigned long long*>(dev_ptr); }
 unsigned long long* stall_counters() { return g_stall_counters; }
 

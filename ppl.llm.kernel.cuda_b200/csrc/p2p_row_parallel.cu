@@ -61,6 +61,9 @@ struct Ctx {
     // second stream and fork / join events of the two-chunk schedule (created with the context)
     cudaStream_t side = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;
+    // local scratch through which the GEMM's CTA pairs share tiles (GemmArgs::sk_ws), one per column chunk: the two
+    // chunks' GEMMs can run at the same time; nullptr = whole tiles only
+    uint8_t* sk_ws = nullptr;
 };
 
 struct Peers {
@@ -402,6 +405,10 @@ int32_t pplb200_p2p_create(int32_t rank, int32_t size, int64_t bytes, void** ctx
         delete c;
         return fail(RC_DEVICE_RUNTIME_ERROR, "stream / event creation failed");
     }
+    if (cudaMalloc((void**)&c->sk_ws, (size_t)(2 * kSkWsBytes)) != cudaSuccess) {
+        c->sk_ws = nullptr; // optional
+        cudaGetLastError();
+    }
     c->peer[rank] = c->base;
     c->connected = size == 1;
     *ctx_out = c;
@@ -469,6 +476,7 @@ int32_t pplb200_p2p_destroy(void* ctx) {
     for (int r = 0; r < c->size; ++r)
         if (c->opened[r]) cudaIpcCloseMemHandle(c->peer[r]);
     cudaFree(c->base);
+    if (c->sk_ws) cudaFree(c->sk_ws);
     if (c->side) cudaStreamDestroy(c->side);
     if (c->fork) cudaEventDestroy(c->fork);
     if (c->join) cudaEventDestroy(c->join);
@@ -539,6 +547,7 @@ int32_t pplb200_i8i8_row_parallel_linear_p2p(pplb200_stream_t stream_, void* ctx
         g.row_absmax_bits = nullptr;
         for (int r = 0; r < size; ++r) g.push_base[r] = reinterpret_cast<int32_t*>(c->peer[r] + recv_off) + col0;
         g.push_rows = (int32_t)Ms; g.push_rank = rank;
+        if (c->sk_ws) { g.sk_ws = c->sk_ws + (chunk ? kSkWsBytes : 0); g.sk_ws_bytes = kSkWsBytes; }
         const int32_t rc = launch_gemm(st, g);
         if (rc != RC_SUCCESS) return rc;
         p2p_signal_kernel<<<1, 32, 0, st>>>(pr, 2 * chunk, chunk == 0 ? 1 : 0);
@@ -631,6 +640,7 @@ int32_t pplb200_i8i8_column_parallel_linear_p2p(pplb200_stream_t stream_, void* 
         g.row_absmax_bits = nullptr;
         for (int r = 0; r < size; ++r) g.push_base[r] = reinterpret_cast<int32_t*>(c->peer[r] + area_off);
         g.gather_ranks = size; g.gather_col0 = (int64_t)rank * Nw;
+        if (c->sk_ws) { g.sk_ws = c->sk_ws; g.sk_ws_bytes = kSkWsBytes; }
         const int32_t rc = launch_gemm(stream, g);
         if (rc != RC_SUCCESS) return rc;
         p2p_signal_kernel<<<1, 32, 0, stream>>>(pr, kFlagRowGathered, 1, kGatherEpochWord);

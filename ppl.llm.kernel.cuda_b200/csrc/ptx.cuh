@@ -93,6 +93,14 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, uint32_t src,
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                  ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
 }
+// 2-D tiled reduction, shared -> global: the box is ADDED element-wise (element type of the tensor map, int32 here) to
+// the tensor by the memory system; same tracking and coordinate rules as the store.
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* m, uint32_t src, int32_t x, int32_t y) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(x), "r"(y) : "memory");
+}
+// orders this thread's completed async-proxy (TMA) memory operations with its later generic-proxy ones, and the reverse
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // returns once at most N of this thread's bulk groups still have to READ their shared-memory source
 template <int N> __device__ __forceinline__ void bulk_wait_group_read() {

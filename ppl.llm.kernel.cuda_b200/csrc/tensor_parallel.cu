@@ -131,6 +131,7 @@ int32_t pplb200_i8i8_column_parallel_linear(pplb200_stream_t stream_, const void
         if (rc != RC_SUCCESS) return rc;
         input = legacy.input;
         weight = legacy.weight;
+        ws = nullptr; ws_bytes = 0; // taken by the re-laid operands
     }
 
     if (!gather_output) { // raw int32 accumulators, no dequant (column_parallel_linear.cu:81-85,136)
@@ -183,6 +184,7 @@ int32_t pplb200_i8i8_row_parallel_linear(pplb200_stream_t stream_, const void* i
         input = legacy.input;
         weight = legacy.weight;
         lda = Kw;
+        ws = nullptr; ws_bytes = 0; // taken by the re-laid operands
     }
 
     if (size == 1)

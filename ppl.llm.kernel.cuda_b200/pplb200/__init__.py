@@ -41,7 +41,7 @@ EXPORTS = [
     "pplb200_i8i8_row_parallel_p2p_bytes", "pplb200_p2p_create", "pplb200_p2p_export", "pplb200_p2p_connect",
     "pplb200_p2p_connect_local", "pplb200_p2p_destroy", "pplb200_p2p_status", "pplb200_i8i8_row_parallel_linear_p2p",
     "pplb200_i8i8_minmax_quantize_fp16_p2p",
-    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters", "pplb200_i8i8_relayout", "pplb200_i8i8_column_parallel_linear_p2p", "pplb200_i8i8_linear_host_workspace_bytes", "pplb200_i8i8_linear_fp16_host",
+    "pplb200_probe_tensor_peak", "pplb200_probe_stream_read", "pplb200_i8i8_gemm_i32", "pplb200_debug_gemm_stall_counters", "pplb200_debug_gemm_tail_split", "pplb200_i8i8_relayout", "pplb200_i8i8_column_parallel_linear_p2p", "pplb200_i8i8_linear_host_workspace_bytes", "pplb200_i8i8_linear_fp16_host",
 ]
 STATIC_SCRATCH_MAX_ROWS = 16384
 
@@ -98,6 +98,8 @@ def _load():
     lib.pplb200_i8i8_relayout.argtypes = [vp, vp, i32, vp, i32, i64, i64, i32]
     lib.pplb200_debug_gemm_stall_counters.argtypes = [vp]
     lib.pplb200_debug_gemm_stall_counters.restype = None
+    lib.pplb200_debug_gemm_tail_split.argtypes = [i32]
+    lib.pplb200_debug_gemm_tail_split.restype = None
     lib.pplb200_probe_stream_read.argtypes = [vp, vp, i64, vp]
     lib.pplb200_nccl_get_unique_id.argtypes = [vp]
     lib.pplb200_nccl_comm_init.argtypes = [vp, i32, i32, ctypes.POINTER(vp)]
@@ -107,7 +109,7 @@ def _load():
     lib.pplb200_layout_offset.restype = i64
     for name in EXPORTS:
         fn = getattr(lib, name)
-        if name != "pplb200_debug_gemm_stall_counters" and fn.restype is ctypes.c_int:
+        if not name.startswith("pplb200_debug_") and fn.restype is ctypes.c_int:
             fn.restype = i32
     return lib
 
@@ -553,6 +555,11 @@ def tensor_peak_probe(mmas_per_cta=8192, sustained_launches=100, with_loads=True
                 how="tcgen05.mma kind::i8, operands resident in shared memory, no loads; %d MMAs per CTA, all SMs; best of 5 "
                     "launches, SM clock read inside the kernel; sustained = %d launches back to back"
                     % (mmas_per_cta, sustained_launches))
+
+
+def gemm_tail_split(enabled):
+    """Diagnostics: switch the column split of the CTA-pair GEMM's last wave of tiles on / off (default on)."""
+    lib.pplb200_debug_gemm_tail_split(1 if enabled else 0)
 
 
 def gemm_stall_profile(fn):

@@ -257,6 +257,48 @@ def test_gemm_requant_epilogue(cuda, oracle, M, N, K):
     assert np.array_equal(yq.cpu().numpy(), ref["yq"])
 
 
+@pytest.mark.parametrize("M,N,K", [(2560, 2048, 4096), (2500, 2032, 4096), (4000, 1296, 7936), (4864, 1024, 4096),
+                                   (2560, 7680, 3072), (2560, 2048, 3200)])
+def test_gemm_tiles_shared_between_pairs(cuda, oracle, M, N, K):
+    """Tile counts that are not a multiple of the 74 CTA pairs (80, 96, 76 and 300 tiles): the K blocks of the last
+    waves are dealt out evenly, so tiles at the border of two pairs' shares are computed in two K segments that meet
+    in the workspace.  All three epilogues must equal the oracle, with the sharing switched off and on, call after
+    call on the same workspace."""
+    import pplb200
+    rng = np.random.default_rng(M + N + K)
+    a = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    b = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    sm = rng.uniform(0.2, 1.0, M).astype(np.float16)
+    sn = (rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)
+    bias = (rng.standard_normal(N) * 0.02).astype(np.float16)
+    ta, tb, tsm, tsn, tbias = _t(cuda, a), _t(cuda, b), _t(cuda, sm), _t(cuda, sn), _t(cuda, bias)
+    exact = _exact_gemm(cuda, ta, tb)
+    acc_np = exact.cpu().numpy()
+    rc, y_ref = oracle.dequantize(acc_np, sm, sn, bias)
+    assert rc == 0
+    rc, yq_ref, ys_ref = oracle.quantize(y_ref)
+    assert rc == 0
+    for r in (0, M - 1):
+        assert np.array_equal(acc_np[r], oracle.gemm_rows(a, b, r, r + 1)[0])
+    ws = cuda.empty((pplb200.gemm_workspace_bytes(M, N, K, pplb200.EPI_DEQUANT_F16_REQUANT_I8),), dtype=cuda.uint8, device="cuda")
+    ws.fill_(0x5a)  # the workspace need not be initialised
+    try:
+        for split in (False, True, True):
+            pplb200.gemm_tail_split(split)
+            acc = pplb200.gemm_i8i8(ta, tb, ws=ws)
+            y = pplb200.gemm_i8i8(ta, tb, mode=pplb200.EPI_DEQUANT_F16, scale_m=tsm, scale_n=tsn, bias=tbias, ws=ws)
+            y2, yq, ys = pplb200.gemm_i8i8(ta, tb, mode=pplb200.EPI_DEQUANT_F16_REQUANT_I8, scale_m=tsm, scale_n=tsn, bias=tbias, ws=ws)
+            cuda.cuda.synchronize()
+            assert pplb200.gemm_status() == 0
+            assert cuda.equal(acc, exact)
+            assert np.array_equal(oracle.f16_bits(y.cpu().numpy()), oracle.f16_bits(y_ref))
+            assert np.array_equal(oracle.f16_bits(y2.cpu().numpy()), oracle.f16_bits(y_ref))
+            assert np.array_equal(yq.cpu().numpy(), yq_ref)
+            assert np.array_equal(oracle.f16_bits(ys.cpu().numpy()), oracle.f16_bits(ys_ref))
+    finally:
+        pplb200.gemm_tail_split(True)
+
+
 def test_gemm_error_codes(cuda):
     import pplb200
     a = cuda.zeros((8, 40), dtype=cuda.int8, device="cuda")

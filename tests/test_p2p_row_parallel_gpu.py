@@ -54,6 +54,7 @@ def _case(torch, pplb200, wl, world, M, K, N, with_bias, rounds=1, seed=0):
     (8, 40, 1024, 72, True),        # 5 rows per owner
     (3, 390, 768, 520, False),      # odd number of ranks
     (1, 300, 512, 256, True),       # a single rank: no exchange
+    (2, 2560, 8192, 2048, True),    # 80 tiles on 74 CTA pairs: tiles shared between pairs as K segments
 ])
 def test_p2p_row_parallel_matches_unsharded(cuda, pplb200, world, M, K, N, with_bias):
     import w8a8_workloads as wl
@@ -168,6 +169,7 @@ def test_sharded_quantizer_matches_unsharded(cuda, pplb200, world, M, K):
     (8, 40, 512, 192, True),        # small batch: 24-column blocks
     (3, 390, 768, 1560, False),     # odd number of ranks
     (1, 130, 512, 264, True),       # a single rank
+    (2, 2560, 4096, 4096, True),    # 80 tiles per rank on 74 CTA pairs: tiles shared between pairs as K segments
 ])
 def test_p2p_column_parallel_gather_matches_unsharded(cuda, pplb200, world, M, K, N, with_bias):
     """Column-parallel linear with gather_output: every rank's GEMM epilogue stores its fp16 block into every
