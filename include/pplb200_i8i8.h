@@ -130,7 +130,12 @@ int32_t pplb200_i8i8_gate_up_swiglu_requant(pplb200_stream_t stream, const void*
                                             void* out_q, void* out_q_scale);
 
 /*
- * Scratch bytes pplb200_i8i8_gemm needs for (M, N, K, mode).  0 means `ws` may be NULL.
+ * Scratch bytes pplb200_i8i8_gemm asks for (M, N, K, mode): the row maxima of mode 2 (required: M * 4 rounded up to
+ * 256) and, for M > 128, about 10.5 MB through which the CTA pairs of the large-batch kernel exchange K slices of
+ * the few tiles left over when the tile count is not a multiple of the pair count (optional: a NULL or smaller
+ * workspace only switches that off; results are the same, the GEMM is up to one wave of tiles slower).  256-byte
+ * aligned, contents need not be initialised, not shared by calls that may run at the same time.  0 means `ws` may be
+ * NULL.
  */
 int64_t pplb200_i8i8_gemm_workspace_bytes(int64_t M, int64_t N, int64_t K, int32_t epilogue_mode);
 

@@ -779,6 +779,13 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     }
 }
 
+__global__ void __launch_bounds__(256) zero_fill_kernel(uint4* dst, int64_t vecs) {
+    const int64_t i0 = (int64_t)blockIdx.x * 1024 + threadIdx.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (i0 + j * 256 < vecs) dst[i0 + j * 256] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 // ---- host side ---------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -934,11 +941,15 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
         int64_t f = pairs / rest;
         if (f > 8) f = 8;
         if (f > p.num_k_blocks / 4) f = p.num_k_blocks / 4; // at least four K blocks per slice
-        // Worth it when the K blocks saved -- (1 - 1/f) of a tile -- outweigh what slicing costs: clearing, adding
-        // to and reading back `rest` scratch tiles, measured at about 1.25 K blocks' time per tile plus a fixed 13.
+        // Worth it when the K blocks saved -- (1 - 1/f) of a tile -- outweigh what slicing costs.  The slice's epilogue
+        // (reduction, waiting for it to be performed, reading the sums back) keeps the epilogue warps busy for about
+        // 28 k cycles against 5 k for a whole tile, which only a long main loop of the following tile hides; measured
+        // over shapes, the cost is about 1.25 K blocks' time per leftover tile plus a fixed 13.
         if (f >= 2 && 4 * (f - 1) * p.num_k_blocks >= f * (52 + 5 * rest)) {
-            if (cudaMemsetAsync(a.sk_ws, 0, (size_t)(kSkStateBytes + rest * kSkTileBytes), stream) != cudaSuccess)
-                return fail(RC_DEVICE_RUNTIME_ERROR, "memset failed");
+            // cleared by a kernel: a memset node between two kernels costs several times as much on the stream
+            const int64_t vecs = (kSkStateBytes + rest * kSkTileBytes) / 16;
+            zero_fill_kernel<<<(unsigned)((vecs + 1023) / 1024), 256, 0, stream>>>(static_cast<uint4*>(a.sk_ws), vecs);
+            if (cudaGetLastError() != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "clearing the slice scratch failed");
             p.sk_arrivals = static_cast<unsigned int*>(a.sk_ws);
             p.sk_scratch = reinterpret_cast<int32_t*>(static_cast<char*>(a.sk_ws) + kSkStateBytes);
             if (!make_output_map(&tsk, p.sk_scratch, rest * 256, 256, 256, 4))
