@@ -454,6 +454,10 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     ptx::cluster_sync_all(); // barriers of both CTAs are initialised before anyone signals them
     ptx::tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    // Launched as a programmatic dependent (fused linear), everything above ran under the tail of the preceding
+    // kernel; its results (quantized activations, row scales, cleared scratch) are needed from here on.  Every
+    // thread waits: all of them read such data.  A no-op in an ordinary launch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int num_pairs = (int)(gridDim.x >> 1);
     const int pair_id = (int)(blockIdx.x >> 1);
@@ -780,6 +784,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
 }
 
 __global__ void __launch_bounds__(256) zero_fill_kernel(uint4* dst, int64_t vecs) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // the GEMM may run its preamble meanwhile
     const int64_t i0 = (int64_t)blockIdx.x * 1024 + threadIdx.x;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
@@ -964,13 +969,15 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     cfg.blockDim = dim3(wide_epilogue ? 64 + 32 * 8 : 64 + 32 * 4, 1, 1);
     cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = 2;
+    attrs[0].val.clusterDim.y = 1;
+    attrs[0].val.clusterDim.z = 1;
+    attrs[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attrs;
+    cfg.numAttrs = a.pdl ? 2 : 1;
     const cudaError_t e = wide_epilogue ? cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<8>, ta, tb, tc, tsk, p)
                                         : cudaLaunchKernelEx(&cfg, gemm_i8_tcgen05_pair_kernel<4>, ta, tb, tc, tsk, p);
     if (e != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "pair GEMM launch failed: %s", cudaGetErrorString(e));
