@@ -61,6 +61,8 @@ struct KernelParams {
     // later tile as k_slices items whose int32 partial tiles are added into sk_scratch[tile - full_tiles][256][256];
     // sk_arrivals[(tile - full_tiles) * 8 + cta * 4 + warp] counts the slices delivered.
     int32_t full_tiles, k_slices;
+    // CTA-pair kernel: tiles are numbered m-tile fastest within groups of group_m m-tiles (see tile_coords)
+    int32_t group_m;
     unsigned int* sk_arrivals;
     int32_t* sk_scratch;
     // EPI_GATHER_F16 (CTA-pair kernel only): see GemmArgs
@@ -358,6 +360,21 @@ gemm_i8_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
 }
 
 
+// Tile number -> (m tile, n tile) of the CTA-pair kernel.  Consecutive numbers run at the same time, so the numbering
+// decides what is live in L2: within a group of group_m m-tiles the m index runs fastest, the n index next, and the
+// groups follow one another.  With one group (all m-tiles) every wave touches the whole activation matrix, which
+// for a large batch does not survive in L2 between waves next to the streaming output; with groups, the group's
+// activation panels stay resident while the weight panels stream past them once per group.
+__device__ __forceinline__ void tile_coords(const KernelParams& p, int tile, int& m_tile, int& n_tile) {
+    const int per_group = p.group_m * p.num_n_tiles;
+    const int g = tile / per_group;
+    const int idx = tile - g * per_group;
+    const int m0 = g * p.group_m;
+    const int gm = p.num_m_tiles - m0 < p.group_m ? p.num_m_tiles - m0 : p.group_m;
+    n_tile = idx / gm;
+    m_tile = m0 + idx - n_tile * gm;
+}
+
 // The work of one CTA pair, in order.  The persistent grid runs in waves of one tile per pair; a tile count that is not
 // a multiple of the pair count would leave most pairs idle during the last wave.  So when few tiles are left over
 // (at most half as many as there are pairs), each of them is cut along K into k_slices items that different pairs
@@ -475,8 +492,8 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             WorkIter work(p, num_tiles, pair_id, num_pairs);
             int tile, kb0, cnt;
             while (ok && work.next(tile, kb0, cnt)) {
-                const int m_tile = tile % p.num_m_tiles;
-                const int n_tile = tile / p.num_m_tiles;
+                int m_tile, n_tile;
+                tile_coords(p, tile, m_tile, n_tile);
                 const int row_a = m_tile * 256 + (int)rank * BM;
                 // SwiGLU: the leader stages 128 "x" weight rows, its partner the 128 "gate" rows of the same
                 // output channels, so accumulator columns [0,128) and [128,256) pair up element by element
@@ -564,8 +581,8 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
         WorkIter work(p, num_tiles, pair_id, num_pairs);
         int tile, kb0, cnt;
         for (; work.next(tile, kb0, cnt); ++it) {
-            const int m_tile = tile % p.num_m_tiles;
-            const int n_tile = tile / p.num_m_tiles;
+            int m_tile, n_tile;
+            tile_coords(p, tile, m_tile, n_tile);
             const uint32_t buf = it & 1, acc_phase = (it >> 1) & 1;
             const long long tw = p.stall ? clock64() : 0;
             if (!ptx::mbar_wait(ptx::smem_addr(&acc_full_bar[buf]), acc_phase, p.status, ST_EPI_TIMEOUT)) break;
@@ -937,6 +954,16 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
     const int64_t tiles = (int64_t)p.num_m_tiles * p.num_n_tiles;
     int64_t pairs = dev.sms / 2;
     if (tiles < pairs) pairs = tiles;
+    // m-tiles per group (see tile_coords): as many activation panels (256 rows x K) as fit in about 32 MB of L2 --
+    // the fewer groups, the fewer passes over the weights -- but at least 9, where a wave's footprint
+    // (group_m + 74 / group_m panels) is smallest.  M8192 K8192 N28672: 16 (1.265 ms with one group of 32, 1.164 ms
+    // with 16, 1.186 with 10, 1.193 with 24; DRAM reads of the one-group form were 2.09 GB for 302 MB of operands).
+    {
+        int64_t gm = (32ll << 20) / (256 * a.K);
+        if (gm < 9) gm = 9;
+        if (gm > p.num_m_tiles) gm = p.num_m_tiles;
+        p.group_m = (int32_t)gm;
+    }
     // Few tiles left over after the full waves: cut them along K (see WorkIter), if the caller's workspace holds the
     // scratch tiles.  Not for SwiGLU (eight epilogue warps, paired accumulator halves).
     p.full_tiles = (int32_t)tiles; p.k_slices = 1;
