@@ -300,6 +300,22 @@ class Workload:
         return "%s-parallel over %d GPUs" % (self.shard, self.world)
 
 
+def _slices_leftover_tiles(M, N, K, pairs=74):
+    """True when the large-batch GEMM of this shape cuts its leftover tiles into K slices, which adds one launch (the
+    kernel that clears the slice scratch) to the step.  Mirrors the launcher's rule in csrc/gemm_i8_tcgen05.cu; only
+    used for the launch count reported as `gpu_launches`."""
+    if M <= 128:
+        return False
+    tiles = ((M + 255) // 256) * ((N + 255) // 256)
+    if tiles < pairs:
+        return False
+    rest, nkb = tiles % pairs, (K + 127) // 128
+    if rest == 0 or rest > 40:
+        return False
+    f = min(pairs // rest, 8, nkb // 4)
+    return f >= 2 and 4 * (f - 1) * nkb >= f * (52 + 5 * rest)
+
+
 def build_ours(wk):
     """Returns (step(i), e2e_step(i), kernel_only(i), launches_per_step, h2d, d2h, gemm_bytes, result(s))."""
     import torch
@@ -342,7 +358,7 @@ def build_ours(wk):
             pplb200.gemm_i8i8(xq, wk.w[s], mode=mode, scale_m=sm, scale_n=wk.sn, bias=wk.bias, ws=gws, out=ys[s])
 
         gemm_bytes = M * K + Nw * K + 2 * Nw + (2 * Nw if wk.bias is not None else 0) + 2 * M + 2 * M * Nw
-        launches = 2 + (1 if requant else 0)
+        launches = 2 + (1 if requant else 0) + (1 if _slices_leftover_tiles(M, Nw, K) else 0)
         return step, e2e, kernel_only, launches, h2d, d2h, gemm_bytes, (lambda s: lins[s].y)
 
     # row parallel: quantize the full activation rows (full-K absmax), GEMM on this rank's K shard,
@@ -435,12 +451,15 @@ def build_ours(wk):
     raw = torch.empty((M, N), dtype=torch.int32, device=dev) if qbuf is None else qbuf
     pplb200.minmax_quantize_fp16(wk.x[0], out=xq_full, scale=sm)  # real operand values for the GEMM timed alone
 
+    gws = torch.empty((max(pplb200.gemm_workspace_bytes(M, N, Kw, pplb200.EPI_RAW_I32), 256),), dtype=torch.uint8, device=dev)
+
     def kernel_only(i):
         s = i % wk.nsets
-        pplb200.gemm_i8i8(xq_full[:, wk.k0:wk.k1], wk.w[s], out=raw)
+        pplb200.gemm_i8i8(xq_full[:, wk.k0:wk.k1], wk.w[s], ws=gws, out=raw)
 
     gemm_bytes = M * Kw + N * Kw + 4 * M * N
-    launches = 6 if wk.row_reduce == "p2p" else 3  # quantizer, GEMM, 2 flag kernels, reduce + dequant, row fetch
+    # quantizer, GEMM, 2 flag kernels, reduce + dequant, row fetch (+ the clearing of the K-slice scratch)
+    launches = (6 if wk.row_reduce == "p2p" else 3) + (1 if _slices_leftover_tiles(M, N, Kw) else 0)
     return step, e2e, kernel_only, launches, h2d, M * N * 2, gemm_bytes, (lambda s: y)
 
 
