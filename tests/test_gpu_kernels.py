@@ -299,6 +299,43 @@ def test_gemm_tiles_shared_between_pairs(cuda, oracle, M, N, K):
         pplb200.gemm_tail_split(True)
 
 
+@pytest.mark.parametrize("M,N,K", [(4400, 1280, 8192), (2560, 2048, 16384), (5000, 1032, 8192), (4608, 4352, 8192)])
+def test_gemm_tile_groups_ragged(cuda, M, N, K):
+    """Large-batch GEMM with more m-tiles than one L2 group holds (groups of 16 at K = 8192, of 9 at K = 16384), the last
+    group ragged (18 = 16 + 2, 10 = 9 + 1, 20 = 16 + 4 m-tiles), together with sliced leftover tiles and a ragged last
+    column tile."""
+    import pplb200
+    torch = cuda
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
+    b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=g)
+    exact = _exact_gemm(torch, a, b)
+    for _ in range(2):
+        c = pplb200.gemm_i8i8(a, b)
+        torch.cuda.synchronize()
+        assert pplb200.gemm_status() == 0
+        assert torch.equal(c, exact)
+
+
+def test_gemm_random_shapes(cuda):
+    """Seeded sweep over shapes of the large-batch kernels (CTA pairs and single CTAs, every tile width, sliced and whole
+    leftover tiles): raw int32 result against the exact product."""
+    import pplb200
+    torch = cuda
+    rng = np.random.default_rng(20240611)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    for _ in range(24):
+        M = int(rng.integers(129, 5200))
+        N = int(rng.integers(1, 700)) * 8
+        K = int(rng.integers(1, 320)) * 16
+        a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda", generator=g)
+        b = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=g)
+        c = pplb200.gemm_i8i8(a, b)
+        torch.cuda.synchronize()
+        assert pplb200.gemm_status() == 0, (M, N, K)
+        assert torch.equal(c, _exact_gemm(torch, a, b)), (M, N, K)
+
+
 def test_gemm_error_codes(cuda):
     import pplb200
     a = cuda.zeros((8, 40), dtype=cuda.int8, device="cuda")
