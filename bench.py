@@ -331,7 +331,7 @@ def build_ours(wk):
             lins[s](wk.x[s])
 
         # end to end through the library's host-buffer entry point (pplb200_i8i8_linear_fp16_host): pinned host
-        # activations in, pinned host results out, copies and compute of consecutive 1024-token chunks overlapped
+        # activations in, pinned host results out, copies and compute of consecutive chunks (128, 128, 256, 512, then 1024 tokens) overlapped
         y_host = torch.empty((M, Nw), dtype=torch.float16).pin_memory()
         yq_host = torch.empty((M, Nw), dtype=torch.int8).pin_memory() if requant else None
         ys_host = torch.empty((M,), dtype=torch.float16).pin_memory() if requant else None
@@ -954,7 +954,7 @@ def main():
         "e2e": {"value": ops_per_step / (res["ms_e2e"] / args.steps * 1e-3) / 1e12, "unit": "TOPS",
                 "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
                 "note": ("activations in / outputs out through pinned host memory each step; weights resident; "
-                         + ("the library's host-buffer entry point (chunks of 1024 tokens: copy in, compute and copy out overlap)"
+                         + ("the library's host-buffer entry point (chunks of 1024 tokens after a ramp of 128, 128, 256, 512: copy in, compute and copy out overlap)"
                             if impl == "ours" and res["shard"] != "row" else "copy in, the operators, copy out, one after the other"))},
         "gpu_launches": res["launches"] * args.steps,
         "clocks": res["clocks"],

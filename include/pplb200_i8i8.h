@@ -214,7 +214,9 @@ int32_t pplb200_i8i8_linear_fp16(pplb200_stream_t stream, const void* x, const v
  * of consecutive chunks -- host -> device copy, quantize + GEMM + epilogue on `stream`, device -> host copy -- run on
  * three streams at once (the two copy streams and their events are created per device at the first call, which
  * therefore should come before any stream capture), so a large batch costs little more than its slower copy
- * direction.  Chunking is exact: the per-token quantizer and the epilogue work row by row.  `ws` is DEVICE memory of
+ * direction; with chunks of 1024 tokens or more the first chunk goes in as chunk_rows / 8, / 8, / 4 and / 2 tokens, so
+ * that the copy out, usually the longest of the three, starts early.  Chunking is exact: the per-token quantizer and
+ * the epilogue work row by row.  `ws` is DEVICE memory of
  * pplb200_i8i8_linear_host_workspace_bytes (two sets of staging buffers); weights, scales and bias are device
  * pointers as in pplb200_i8i8_linear_fp16.  Work enqueued on `stream` after the call runs after the last copy out.
  * No counterpart in the reference, whose operators take device pointers only.

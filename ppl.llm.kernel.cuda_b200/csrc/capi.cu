@@ -420,10 +420,16 @@ int32_t pplb200_i8i8_linear_fp16_host(pplb200_stream_t stream_, const void* x_ho
     PPLB200_CU(cudaEventRecord(h->start, stream));
     PPLB200_CU(cudaStreamWaitEvent(h->in, h->start, 0));
     PPLB200_CU(cudaStreamWaitEvent(h->out, h->start, 0));
-    int64_t chunk = 0;
-    for (int64_t m0 = 0; m0 < M; m0 += c, ++chunk) {
+    // Chunk sizes: the copy-out of the results is the longest of the three pipelines (PCIe, fp16 [rows, N]), and it can
+    // only start once the first chunk has been copied in and computed.  So the first full chunk is fed in as c/8, c/8,
+    // c/4, c/2 rows (each step's copy-in + compute still fits under the previous step's copy-out), which starts the
+    // copy-out after an eighth of the fill time.
+    const bool ramp = c >= 1024 && M >= 2 * c;
+    int64_t chunk = 0, rows = 0;
+    for (int64_t m0 = 0; m0 < M; m0 += rows, ++chunk) {
         const int b = (int)(chunk & 1);
-        const int64_t rows = M - m0 < c ? M - m0 : c;
+        rows = !ramp || chunk >= 4 ? c : chunk < 2 ? c / 8 : chunk == 2 ? c / 4 : c / 2;
+        if (rows > M - m0) rows = M - m0;
         // copy-in: the staging buffer is free once the linear of two chunks ago has read it
         if (chunk >= 2) PPLB200_CU(cudaStreamWaitEvent(h->in, h->comp_done[b], 0));
         PPLB200_CU(cudaMemcpyAsync(xd[b], (const char*)x_host + m0 * K * 2, (size_t)(rows * K * 2), cudaMemcpyHostToDevice, h->in));

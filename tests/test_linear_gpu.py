@@ -132,7 +132,8 @@ def test_linear_error_codes(cuda):
 
 
 @pytest.mark.parametrize("M,K,N,chunk,requant", [(300, 512, 264, 128, False), (2500, 1024, 1032, 1024, False),
-                                                 (96, 512, 272, 0, True), (1100, 256, 512, 256, True)])
+                                                 (96, 512, 272, 0, True), (1100, 256, 512, 256, True),
+                                                 (2200, 512, 528, 1024, True)])  # the last: short first chunks + re-quantize
 def test_linear_on_host_buffers_matches_device_path(cuda, oracle, M, K, N, chunk, requant):
     """pplb200_i8i8_linear_fp16_host: pinned host activations in, pinned host results out, chunks of the batch
     overlapped on three streams.  Bit-identical to the device-buffer linear (chunking is exact: every step works
