@@ -865,6 +865,53 @@ def aux_kernels(steps, warmup):
         tiles = -(-M // 256) * -(-N // 256)
         st["mma_thread_cycles_per_k_block"] = round(st["mma_thread_cycles"] / (tiles / 74.0 * (K // 128)), 1)
     out["pair_gemm_thread_waits_c2"] = st
+    del a, b, y
+    torch.cuda.empty_cache()
+
+    # Leftover tiles: GEMM + fused dequant of shapes whose tile count is not a multiple of the 74 CTA pairs, with the K
+    # slicing of the leftover tiles switched off and on (debug switch of the library); launches replayed from a CUDA
+    # graph over enough operand sets to exceed L2.  The first two shapes are c4's and c2's shards on 8 GPUs.
+    slices = {}
+    for (M, N, K) in ((8192, 3584, 8192), (4096, 2752, 4096), (8192, 3328, 8192), (2048, 8192, 28672)):
+        nset = max(2, int(200e6 // (N * K + M * K)) + 1)
+        As = [torch.randint(-127, 128, (M, K), generator=g, device="cuda", dtype=torch.int8) for _ in range(nset)]
+        Bs = [torch.randint(-127, 128, (N, K), generator=g, device="cuda", dtype=torch.int8) for _ in range(nset)]
+        sm_ = (torch.rand(M, device="cuda") + 0.5).half()
+        sn_ = (torch.rand(N, device="cuda") * 1e-2 + 1e-3).half()
+        ys = [torch.empty((M, N), dtype=torch.float16, device="cuda") for _ in range(nset)]
+        ws = torch.empty((pplb200.gemm_workspace_bytes(M, N, K, pplb200.EPI_DEQUANT_F16),), dtype=torch.uint8, device="cuda")
+        graphs = {}
+        try:
+            for on in (False, True):
+                pplb200.gemm_tail_split(on)
+                run = lambda: [pplb200.gemm_i8i8(As[i], Bs[i], mode=pplb200.EPI_DEQUANT_F16, scale_m=sm_, scale_n=sn_, ws=ws, out=ys[i])
+                               for i in range(nset)]
+                run()
+                torch.cuda.synchronize()
+                gr = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gr):
+                    run()
+                graphs[on] = gr
+        finally:
+            pplb200.gemm_tail_split(True)
+        times = {False: [], True: []}
+        for it in range(12):
+            for on in (False, True):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                graphs[on].replay()
+                e1.record()
+                torch.cuda.synchronize()
+                if it >= 4:
+                    times[on].append(e0.elapsed_time(e1) * 1e3 / nset)
+        tiles = -(-M // 256) * -(-N // 256)
+        med = lambda v: sorted(v)[len(v) // 2]
+        slices["M%d N%d K%d" % (M, N, K)] = {"tiles": tiles, "waves": round(tiles / 74.0, 2), "leftover_tiles": tiles % 74,
+                                              "sliced_by_default": _slices_leftover_tiles(M, N, K),
+                                              "whole_tiles_us": round(med(times[False]), 1), "default_us": round(med(times[True]), 1)}
+        del As, Bs, ys, ws, graphs
+        torch.cuda.empty_cache()
+    out["leftover_tile_slices"] = slices
     return out
 
 
