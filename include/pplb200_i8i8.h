@@ -400,7 +400,8 @@ void pplb200_debug_gemm_stall_counters(void* counters);
  * Diagnostics (process-wide switch, not thread-safe, on by default): when few 256 x 256 output tiles are left over
  * after the full waves of one tile per CTA pair, the CTA-pair GEMM cuts them along K into slices that different pairs
  * compute at once and sums the slices in the workspace (integer sums: the result does not depend on it).
- * enabled = 0 computes every tile on one pair, for A/B timing.
+ * enabled = 0 computes every tile on one pair, 1 (the default) lets the launcher weigh the K blocks saved against the
+ * cost of the exchange, 2 slices whenever the shape and the workspace allow it; for A/B timing.
  */
 void pplb200_debug_gemm_tail_split(int32_t enabled);
 

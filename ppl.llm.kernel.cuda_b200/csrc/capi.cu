@@ -459,7 +459,7 @@ int32_t pplb200_i8i8_linear_fp16_host(pplb200_stream_t stream_, const void* x_ho
 
 int32_t pplb200_i8i8_gemm_status(int32_t reset) { return gemm_status(reset); }
 void pplb200_debug_gemm_stall_counters(void* counters) { set_stall_counters(counters); }
-void pplb200_debug_gemm_tail_split(int32_t enabled) { set_tail_split(enabled != 0); }
+void pplb200_debug_gemm_tail_split(int32_t enabled) { set_tail_split(enabled < 0 ? 0 : enabled > 2 ? 2 : enabled); }
 
 // Host helper for tests: the library's (row, col) -> offset map for a layout.
 int64_t pplb200_layout_offset(int32_t layout, int64_t rows, int64_t cols, int64_t row, int64_t col) {

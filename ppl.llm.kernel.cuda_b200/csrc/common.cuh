@@ -143,7 +143,7 @@ int32_t launch_gemm_decode(cudaStream_t stream, const GemmArgs& a, unsigned int*
 int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a);
 int32_t gemm_status(int32_t reset);
 void set_stall_counters(void* dev_ptr);
-void set_tail_split(bool on);
+void set_tail_split(int mode);
 unsigned long long* stall_counters();
 
 } // namespace pplb200

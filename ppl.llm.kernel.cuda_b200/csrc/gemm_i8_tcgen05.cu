@@ -126,17 +126,38 @@ constexpr int EPI_STAGE_BYTES = 4 * 2 * 4096;
 
 // accumulator columns c .. c + 31 of this lane's row: from tensor memory, or (sums != nullptr) from this lane's row
 // of a K-sliced tile's summed int32 scratch (written by other SMs' reductions: loads that bypass L1)
+__device__ __forceinline__ void load_sums32(const int32_t* sums, int c, int4 (&v)[8]) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldcg(reinterpret_cast<const int4*>(sums + c) + j);
+}
 __device__ __forceinline__ void load_acc32(uint32_t taddr_row, const int32_t* sums, int c, uint32_t (&acc)[32]) {
     if (sums == nullptr) {
         ptx::tmem_ld_32x32(taddr_row + c, acc);
         ptx::tmem_ld_wait();
     } else {
+        int4 v[8];
+        load_sums32(sums, c, v);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-            const int4 v = __ldcg(reinterpret_cast<const int4*>(sums + c) + j);
-            acc[4 * j] = (uint32_t)v.x; acc[4 * j + 1] = (uint32_t)v.y; acc[4 * j + 2] = (uint32_t)v.z; acc[4 * j + 3] = (uint32_t)v.w;
+            acc[4 * j] = (uint32_t)v[j].x; acc[4 * j + 1] = (uint32_t)v[j].y; acc[4 * j + 2] = (uint32_t)v[j].z; acc[4 * j + 3] = (uint32_t)v[j].w;
         }
     }
+}
+// the same with the scratch columns fetched one step ahead: `ahead` holds columns c .. c + 31 on entry and, when there
+// is a next step, columns c + 32 .. c + 63 on return, so that their latency runs under this step's epilogue work
+__device__ __forceinline__ void load_acc32_ahead(uint32_t taddr_row, const int32_t* sums, int c, bool more, int4 (&ahead)[8],
+                                                 uint32_t (&acc)[32]) {
+    if (sums == nullptr) {
+        ptx::tmem_ld_32x32(taddr_row + c, acc);
+        ptx::tmem_ld_wait();
+        return;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        acc[4 * j] = (uint32_t)ahead[j].x; acc[4 * j + 1] = (uint32_t)ahead[j].y;
+        acc[4 * j + 2] = (uint32_t)ahead[j].z; acc[4 * j + 3] = (uint32_t)ahead[j].w;
+    }
+    if (more) load_sums32(sums, c + 32, ahead);
 }
 
 // Drains this warp's 32 lanes x BN accumulator columns (TMEM address taddr_row) for output rows
@@ -150,13 +171,15 @@ __device__ __forceinline__ void drain_tile(const KernelParams& p, const CUtensor
     const int row = row0 + lane;
     const bool row_ok = row < p.M;
     const uint32_t my_row = (uint32_t)lane * 128u, sw = (uint32_t)(lane & 7);
+    int4 ahead[8];
+    if (sums != nullptr) load_sums32(sums, 0, ahead);
     if (p.mode == EPI_RAW_I32) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += 32) {
             const int n0 = n_base + c0;
             if (n0 >= p.N) break; // warp-uniform
             uint32_t acc[32];
-            load_acc32(taddr_row, sums, c0, acc);
+            load_acc32_ahead(taddr_row, sums, c0, c0 + 32 < BN, ahead, acc);
             if (p.raw_affine) {
                 const int32_t* old = reinterpret_cast<const int32_t*>(p.out) + (int64_t)row * p.ldc + n0;
 #pragma unroll
@@ -203,7 +226,7 @@ __device__ __forceinline__ void drain_tile(const KernelParams& p, const CUtensor
             const int nn = n0 + 32 * h;
             if (nn >= p.N) break; // warp-uniform; the box is clipped at column N
             uint32_t acc[32];
-            load_acc32(taddr_row, sums, c0 + 32 * h, acc);
+            load_acc32_ahead(taddr_row, sums, c0 + 32 * h, c0 + 32 * h + 32 < BN, ahead, acc);
 #pragma unroll
             for (int j = 0; j < 32; j += 8) {
                 if (nn + j >= p.N) break;
@@ -855,7 +878,7 @@ bool make_output_map(CUtensorMap* map, void* base, int64_t M, int64_t N, int64_t
 }
 
 // Diagnostics switch (pplb200_debug_gemm_tail_split): false = whole tiles only, whatever the tile count.
-bool g_slice_leftover_tiles = true;
+int g_slice_leftover_tiles = 1; // 0 off, 1 by the launcher's rule, 2 whenever possible
 
 // Diagnostics switch (pplb200_debug_gemm_stall_counters): device array the CTA-pair kernel fills when non-null.
 unsigned long long* g_stall_counters = nullptr;
@@ -977,7 +1000,7 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
         // (reduction, waiting for it to be performed, reading the sums back) keeps the epilogue warps busy for about
         // 28 k cycles against 5 k for a whole tile, which only a long main loop of the following tile hides; measured
         // over shapes, the cost is about 1.25 K blocks' time per leftover tile plus a fixed 13.
-        if (f >= 2 && 4 * (f - 1) * p.num_k_blocks >= f * (52 + 5 * rest)) {
+        if (f >= 2 && (g_slice_leftover_tiles == 2 || 4 * (f - 1) * p.num_k_blocks >= f * (52 + 5 * rest))) {
             // cleared by a kernel: a memset node between two kernels costs several times as much on the stream
             const int64_t vecs = (kSkStateBytes + rest * kSkTileBytes) / 16;
             zero_fill_kernel<<<(unsigned)((vecs + 1023) / 1024), 256, 0, stream>>>(static_cast<uint4*>(a.sk_ws), vecs);
@@ -1037,7 +1060,7 @@ int32_t launch_gemm(cudaStream_t stream, const GemmArgs& a) {
     return launch_bn<64>(stream, a, *dev);
 }
 
-void set_tail_split(bool on) { g_slice_leftover_tiles = on; }
+void set_tail_split(int mode) { g_slice_leftover_tiles = mode; }
 void set_stall_counters(void* dev_ptr) { g_stall_counters = static_cast<unsigned long long*>(dev_ptr); }
 unsigned long long* stall_counters() { return g_stall_counters; }
 

@@ -559,7 +559,7 @@ def tensor_peak_probe(mmas_per_cta=8192, sustained_launches=100, with_loads=True
 
 def gemm_tail_split(enabled):
     """Diagnostics: switch the column split of the CTA-pair GEMM's last wave of tiles on / off (default on)."""
-    lib.pplb200_debug_gemm_tail_split(1 if enabled else 0)
+    lib.pplb200_debug_gemm_tail_split(int(enabled))  # 0 off, 1 (True) by the launcher's rule, 2 whenever possible
 
 
 def gemm_stall_profile(fn):
