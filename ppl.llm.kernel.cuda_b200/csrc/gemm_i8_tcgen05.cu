@@ -512,6 +512,10 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
             long long t_wait = 0;
             const long long t_begin = clock64();
             const uint32_t full_local0 = ptx::smem_addr(&full_bar[0]), full_leader0 = ptx::map_to_cta(full_local0, 0);
+            // Activation panels are what the following waves of the group come back to; the weight panels and the output
+            // stream past them.  Marked evict-last they stay (c4 -1 %, c3 -2 %; with both operands hinted, or with the
+            // weights marked evict-first, nothing or worse).
+            const uint64_t pol_a = ptx::l2_policy_evict_last();
             WorkIter work(p, num_tiles, pair_id, num_pairs);
             int tile, kb0, cnt;
             while (ok && work.next(tile, kb0, cnt)) {
@@ -531,7 +535,7 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
                     if (p.stall) t_wait += clock64() - tw;
                     const uint32_t sa = ring + stage * C::STAGE_BYTES;
                     if (leader) ptx::mbar_arrive_expect_tx(full_local0 + stage * 8u, 2 * C::STAGE_BYTES);
-                    ptx::tma_load_2d_pair(sa, &tmap_a, full_leader0 + stage * 8u, kb * BK, row_a);
+                    ptx::tma_load_2d_pair_hint(sa, &tmap_a, full_leader0 + stage * 8u, kb * BK, row_a, pol_a);
                     ptx::tma_load_2d_pair(sa + C::A_BYTES, &tmap_b, full_leader0 + stage * 8u, kb * BK, row_b);
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                 }
