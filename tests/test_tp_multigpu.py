@@ -81,8 +81,9 @@ def _worker(rank, world, tmp):
 
     rng = np.random.default_rng(123)  # same inputs on every rank
     results = {}
-    # the last shape is large enough for the peer-memory path's two-chunk schedule (second stream)
-    for (M, K, N) in [(64, 1024, 512), (300, 2048, 1536), (1024, 1024, 768), (33, 512, 256), (2048, 2048, 8192)]:
+    # (2048, 2048, 8192) is large enough for the peer-memory path's two-chunk schedule (second stream); the last shape
+    # gives 80 output tiles on 74 CTA pairs with a K shard long enough (on 2 GPUs) for the leftover tiles to be sliced
+    for (M, K, N) in [(64, 1024, 512), (300, 2048, 1536), (1024, 1024, 768), (33, 512, 256), (2048, 2048, 8192), (2560, 8192, 2048)]:
         x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float16)).cuda()
         w = torch.from_numpy(rng.integers(-127, 128, (N, K), dtype=np.int8)).cuda()
         sn = torch.from_numpy((rng.uniform(0.001, 0.01, N) * 8192).astype(np.float16)).cuda()
