@@ -827,12 +827,17 @@ gemm_i8_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __
     }
 }
 
+// Clears the K-slice scratch.  In the fused linear it is launched as a programmatic dependent of the quantizer: it
+// depends on nothing the quantizer writes, so it runs under the quantizer's last wave -- but it only EXITS after the
+// quantizer has completed (the wait below), because the GEMM, its own programmatic dependent, takes the completion of
+// this grid as its licence to read the quantizer's output.
 __global__ void __launch_bounds__(256) zero_fill_kernel(uint4* dst, int64_t vecs) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); // the GEMM may run its preamble meanwhile
     const int64_t i0 = (int64_t)blockIdx.x * 1024 + threadIdx.x;
 #pragma unroll
     for (int j = 0; j < 4; ++j)
         if (i0 + j * 256 < vecs) dst[i0 + j * 256] = make_uint4(0u, 0u, 0u, 0u);
+    asm volatile("griddepcontrol.wait;" ::: "memory"); // a no-op in an ordinary launch
 }
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -1007,8 +1012,17 @@ int32_t launch_pair(cudaStream_t stream, const GemmArgs& a, const DeviceInfo& de
         if (f >= 2 && (g_slice_leftover_tiles == 2 || 4 * (f - 1) * p.num_k_blocks >= f * (52 + 5 * rest))) {
             // cleared by a kernel: a memset node between two kernels costs several times as much on the stream
             const int64_t vecs = (kSkStateBytes + rest * kSkTileBytes) / 16;
-            zero_fill_kernel<<<(unsigned)((vecs + 1023) / 1024), 256, 0, stream>>>(static_cast<uint4*>(a.sk_ws), vecs);
-            if (cudaGetLastError() != cudaSuccess) return fail(RC_DEVICE_RUNTIME_ERROR, "clearing the slice scratch failed");
+            cudaLaunchConfig_t zc = {};
+            zc.gridDim = dim3((unsigned)((vecs + 1023) / 1024), 1, 1);
+            zc.blockDim = dim3(256, 1, 1);
+            zc.stream = stream;
+            cudaLaunchAttribute za;
+            za.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            za.val.programmaticStreamSerializationAllowed = 1;
+            zc.attrs = &za;
+            zc.numAttrs = a.pdl ? 1 : 0;
+            if (cudaLaunchKernelEx(&zc, zero_fill_kernel, static_cast<uint4*>(a.sk_ws), vecs) != cudaSuccess)
+                return fail(RC_DEVICE_RUNTIME_ERROR, "clearing the slice scratch failed: %s", cudaGetErrorString(cudaGetLastError()));
             p.sk_arrivals = static_cast<unsigned int*>(a.sk_ws);
             p.sk_scratch = reinterpret_cast<int32_t*>(static_cast<char*>(a.sk_ws) + kSkStateBytes);
             if (!make_output_map(&tsk, p.sk_scratch, rest * 256, 256, 256, 4))
